@@ -68,13 +68,14 @@ class _Group:
     chunk: Optional[int]
     pool: PagePool
     table: np.ndarray          # [max_slots, max_blocks] int32, -1 where no page
+    kept_blocks: int = 0       # leading blocks that a window never gives back (they hold the first tokens every query may read)
 
 
 @dataclass
 class _Request:
     slot: int
     length: int = 0
-    # per group: number of leading blocks already given back (window) and blocks reserved so far
+    # per group: blocks already given back (window; the blocks after the group's kept first ones) and blocks reserved so far
     released: List[int] = None
     reserved: List[int] = None
 
@@ -119,7 +120,8 @@ class CacheManager:
                 key_to_group[key] = len(self.groups)
                 self.groups.append(_Group(key, need.kv_heads, need.head_dim, need.window, need.chunk,
                                           PagePool(num_pages[len(self.groups)], len(self.groups)),
-                                          np.full((max_slots, self.max_blocks), -1, dtype=np.int32)))
+                                          np.full((max_slots, self.max_blocks), -1, dtype=np.int32),
+                                          -(-need.keep_first // page_size) if need.window is not None else 0))
             self._entry_group.append(key_to_group[key])
         # groups that give pages back early
         self._windowed = [gi for gi, g in enumerate(self.groups) if g.window is not None or g.chunk is not None]
@@ -183,16 +185,18 @@ class CacheManager:
         return out
 
     @staticmethod
-    def most_pages_of_a_request(window: Optional[int], page_size: int, length: int, portion: int, chunk: Optional[int] = None) -> int:
+    def most_pages_of_a_request(window: Optional[int], page_size: int, length: int, portion: int, chunk: Optional[int] = None,
+                                kept_blocks: int = 0) -> int:
         """The most pages one request holds at a time in a group: all of its ``length`` tokens, or, behind a window,
-        what a step of at most ``portion`` new tokens can still read (pages the window has passed were given back).
+        what a step of at most ``portion`` new tokens can still read (pages the window has passed were given back),
+        plus the ``kept_blocks`` first pages such a group never gives back.
         A query that reads only its own block of ``chunk`` positions reaches back fewer than ``chunk`` keys, so such a
         group counts like one with that window."""
         full = -(-length // page_size)
         reach = min([w for w in (window, chunk) if w is not None], default=None)
         if reach is None:
             return full
-        return min(full, (reach + max(portion, 1) - 2) // page_size + 2)
+        return min(full, (reach + max(portion, 1) - 2) // page_size + 2 + kept_blocks)
 
     def pool_pages(self) -> List[int]:
         return [g.pool.num_pages for g in self.groups]
@@ -202,7 +206,7 @@ class CacheManager:
 
     def peak_pages(self, length: int, portion: int) -> List[int]:
         """Per group: the most pages a request that grows to ``length`` tokens, at most ``portion`` a step, holds at once."""
-        return [self.most_pages_of_a_request(g.window, self.page_size, length, portion, g.chunk) for g in self.groups]
+        return [self.most_pages_of_a_request(g.window, self.page_size, length, portion, g.chunk, g.kept_blocks) for g in self.groups]
 
     def pages_held(self, rid: Hashable) -> List[int]:
         """Per group: pages the request holds now (what closing it gives back)."""
@@ -357,11 +361,12 @@ class CacheManager:
         for gi in self._windowed:
             g = self.groups[gi]
             first = min(self._first_needed_block(g, new_len), r.reserved[gi])
-            if first > r.released[gi]:
-                pages = [int(p) for p in g.table[r.slot, r.released[gi]: first]]
+            kb = g.kept_blocks
+            if first - kb > r.released[gi]:
+                pages = [int(p) for p in g.table[r.slot, kb + r.released[gi]: first]]
                 g.pool.give_back(pages, rid)
-                g.table[r.slot, r.released[gi]: first] = -1
-                r.released[gi] = first
+                g.table[r.slot, kb + r.released[gi]: first] = -1
+                r.released[gi] = first - kb
 
     def commit_many(self, batch: Sequence[Tuple[Hashable, int]]) -> None:
         """``commit`` for every (request, new length) of a step."""
@@ -376,7 +381,7 @@ class CacheManager:
     def close(self, rid: Hashable) -> None:
         r = self._requests.pop(rid)
         for gi, g in enumerate(self.groups):
-            pages = [int(p) for p in g.table[r.slot, r.released[gi]: r.reserved[gi]]]
+            pages = [int(p) for p in g.table[r.slot, : r.reserved[gi]] if p >= 0]
             g.pool.give_back(pages, rid)
             g.table[r.slot, :] = -1
         self._free_slots.append(r.slot)
@@ -400,10 +405,11 @@ class CacheManager:
             seen = {}
             for rid, r in self._requests.items():
                 row = g.table[r.slot]
-                live = [int(p) for p in row[r.released[gi]: r.reserved[gi]]]
+                kb = min(g.kept_blocks, r.reserved[gi]) if r.released[gi] else 0      # (nothing given back: one live range)
+                live = [int(p) for p in row[:kb]] + [int(p) for p in row[kb + r.released[gi]: r.reserved[gi]]]
                 if any(p < 0 for p in live):
                     raise AssertionError(f"request {rid!r} has a hole in its live blocks")
-                if any(int(p) >= 0 for p in row[: r.released[gi]]) or any(int(p) >= 0 for p in row[r.reserved[gi]:]):
+                if any(int(p) >= 0 for p in row[kb: kb + r.released[gi]]) or any(int(p) >= 0 for p in row[r.reserved[gi]:]):
                     raise AssertionError(f"request {rid!r} has table entries outside its live range")
                 for p in live:
                     if p in seen:

@@ -71,6 +71,7 @@ struct Params {
   int H, Hkv, G, ps, num_pages;
   int ps_shift;     // log2(ps) if ps is a power of two, else -1: a shift in place of a division in the key loops
   float scale_log2; int window;
+  int keep_first;        // with a window: keys below this stay visible to every later query (0: none)
   const float* slopes;   // one per query head, or null: slope * (position - key) is taken off a score (in the score's own units)
   int chunk;             // > 0: a query sees only the keys from floor(position / chunk) * chunk on
   float cap_over_scale;  // > 0: a scaled score s becomes c * tanh(s / c), c the cap, before any bias; kept here as c / scale, so
@@ -261,6 +262,10 @@ __global__ void __launch_bounds__(THREADS, (D <= 64 ? 4 : 1)) attention_wide_ker
   const bool by_distance = p.slopes != nullptr || p.chunk > 0 || capped;     // every score takes the masked path
   const int free_lo = by_distance ? 0x7fffffff : (p.window > 0 ? max(lo, p0 + row_last / G - p.window + 1) : lo);
   const int free_hi = by_distance ? 0 : min(hi, p0 + tok_first + 1);
+  // The first keys that stay visible behind the window: those below the window's first tile come as tiles of their own,
+  // ahead of the others (tiles 0 .. n_keep-1 hold keys [0, keep_end)); those inside the first tile are fetched with it.
+  const int keep = p.window > 0 ? p.keep_first : 0;
+  const int keep_end = min(keep, lo);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, tq = lane & 3;
   const int* bt = p.block_table + (size_t)r * p.bt_width;
@@ -274,9 +279,11 @@ __global__ void __launch_bounds__(THREADS, (D <= 64 ? 4 : 1)) attention_wide_ker
     cp_async16(Qs + row * LDS + ch * 8, p.qkv + (size_t)(q0 + tok) * p.q_stride + (size_t)hd * D + ch * 8, ok);
   }
   const int kt0 = (lo / BN) * BN;
-  const int n_tiles = (hi - kt0 + BN - 1) / BN;
+  const int n_keep = min((keep_end + BN - 1) / BN, kt0 / BN);
+  const int lo_main = keep_end > kt0 ? kt0 : lo;                // first key the window's own tiles fetch
+  const int n_tiles = n_keep + (hi - kt0 + BN - 1) / BN;
   {
-    const int b_lo = lo / p.ps, b_hi = min((hi - 1) / p.ps, p.bt_width - 1);
+    const int b_lo = (n_keep > 0 ? 0 : lo_main) / p.ps, b_hi = min((hi - 1) / p.ps, p.bt_width - 1);
     if (b_hi - b_lo + 1 <= BT_CACHE) {
       for (int i = tid; i <= b_hi - b_lo; i += THREADS) bt_s[i] = bt[b_lo + i];
       __syncthreads();
@@ -285,7 +292,8 @@ __global__ void __launch_bounds__(THREADS, (D <= 64 ? 4 : 1)) attention_wide_ker
     }
   }
   constexpr int stage_elems = (SHARED ? 1 : 2) * BN * LDS;      // keys that are the values too need no second tile
-  load_kv_tile<SHARED>(p, bt, bt_first, hk, kt0, lo, hi, KVs, KVs + BN * LDS);
+  if (n_keep > 0) load_kv_tile<SHARED>(p, bt, bt_first, hk, 0, 0, keep_end, KVs, KVs + BN * LDS);
+  else load_kv_tile<SHARED>(p, bt, bt_first, hk, kt0, lo_main, hi, KVs, KVs + BN * LDS);
   cp_async_commit();
 
   const int row_a = m0 + warp * 16 + g, row_b = row_a + 8;
@@ -301,12 +309,15 @@ __global__ void __launch_bounds__(THREADS, (D <= 64 ? 4 : 1)) attention_wide_ker
   float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.f, l_b = 0.f;
 
   for (int it = 0; it < n_tiles; ++it) {
-    const int kt = kt0 + it * BN;
+    const bool kept_tile = it < n_keep;
+    const int kt = kept_tile ? it * BN : kt0 + (it - n_keep) * BN;
+    const int t_lo = kept_tile ? 0 : lo_main, t_hi = kept_tile ? keep_end : hi;      // keys of this tile that were fetched
     bf16* Ks = KVs + (it & 1) * stage_elems;
     bf16* Vs = SHARED ? Ks : Ks + BN * LDS;
     if (it + 1 < n_tiles) {
       bf16* Kn = KVs + ((it + 1) & 1) * stage_elems;
-      load_kv_tile<SHARED>(p, bt, bt_first, hk, kt + BN, lo, hi, Kn, Kn + BN * LDS);
+      if (it + 1 < n_keep) load_kv_tile<SHARED>(p, bt, bt_first, hk, kt + BN, 0, keep_end, Kn, Kn + BN * LDS);
+      else load_kv_tile<SHARED>(p, bt, bt_first, hk, kt0 + (it + 1 - n_keep) * BN, lo_main, hi, Kn, Kn + BN * LDS);
       cp_async_commit();
       cp_async_wait<1>();
     } else {
@@ -338,7 +349,7 @@ __global__ void __launch_bounds__(THREADS, (D <= 64 ? 4 : 1)) attention_wide_ker
       }
     }
     float mx_a = -INFINITY, mx_b = -INFINITY;
-    if (kt >= free_lo && kt + BN <= free_hi) {
+    if (!kept_tile && kt >= free_lo && kt + BN <= free_hi) {
       // (rows beyond M hold zero queries; what they compute is finite and never stored)
 #pragma unroll
       for (int j = 0; j < NT; ++j) {
@@ -359,9 +370,9 @@ __global__ void __launch_bounds__(THREADS, (D <= 64 ? 4 : 1)) attention_wide_ker
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
           const int key = kt + j * 8 + tq * 2 + e;
-          const bool in_range = key >= lo && key < hi;
-          const bool ok_a = in_range && key <= pos_a && key >= first_a && (p.window <= 0 || key > pos_a - p.window);
-          const bool ok_b = in_range && key <= pos_b && key >= first_b && (p.window <= 0 || key > pos_b - p.window);
+          const bool in_range = key >= t_lo && key < t_hi;
+          const bool ok_a = in_range && key <= pos_a && key >= first_a && (p.window <= 0 || key > pos_a - p.window || key < keep);
+          const bool ok_b = in_range && key <= pos_b && key >= first_b && (p.window <= 0 || key > pos_b - p.window || key < keep);
           s[j][e] = ok_a ? s[j][e] * p.scale_log2 - slope_a * (float)(pos_a - key) : -INFINITY;
           s[j][2 + e] = ok_b ? s[j][2 + e] * p.scale_log2 - slope_b * (float)(pos_b - key) : -INFINITY;
           mx_a = fmaxf(mx_a, s[j][e]);
@@ -539,6 +550,10 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_deep_kernel(const Param
   int lo = p.window > 0 ? max(0, p0 - p.window + 1) : 0;
   if (OPTS && p.chunk > 0) lo = max(lo, (p0 / p.chunk) * p.chunk);
   int hi = p0 + (M - 1) / G + 1;
+  // The first keys that stay visible behind the window, as far as they lie before the window's first key: the first
+  // split takes them as sub-tiles of their own, ahead of its others.
+  const int keep = (OPTS && p.window > 0) ? p.keep_first : 0;
+  const int keep_end = split == 0 ? min(keep, lo) : 0;
   {
     // the request's keys are shared out evenly over the launch's splits, in units of one step of all the block's
     // warps. The splits start at the unit boundary at or below the first key, so their size is taken from there:
@@ -573,9 +588,12 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_deep_kernel(const Param
     }
     return;
   }
+  const int k_first = (lo / DKW) * DKW;
+  const int n_keep = min((keep_end + DKW - 1) / DKW, k_first / DKW);   // sub-tiles of kept keys wholly before the split's first
+  const int lo_main = keep_end > k_first ? k_first : lo;        // first key the split's own sub-tiles fetch
   {
     // lengths and block tables are the step's own inputs: fetched while the kernel before this one finishes
-    const int b_lo = lo / p.ps, b_hi = min((hi - 1) / p.ps, p.bt_width - 1);
+    const int b_lo = (n_keep > 0 ? 0 : lo_main) / p.ps, b_hi = min((hi - 1) / p.ps, p.bt_width - 1);
     if (b_hi - b_lo + 1 <= BT_CACHE) {
       for (int i = tid; i <= b_hi - b_lo; i += NTHR) bt_s[i] = bt[b_lo + i];
       bt = bt_s;
@@ -595,15 +613,18 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_deep_kernel(const Param
   __syncthreads();                                              // queries and table entries are in shared memory
 
   const bool same_page = (p.ps % DKW) == 0;
-  const int k_first = (lo / DKW) * DKW;
-  const int n_sub = (hi - k_first + DKW - 1) / DKW;             // sub-tiles of the split
+  const int n_sub = n_keep + (hi - k_first + DKW - 1) / DKW;    // sub-tiles of the split
+  // sub-tile n of the split: its first key, and the range of keys it fetches
+  auto sub_first = [&](int n) { return n < n_keep ? n * DKW : k_first + (n - n_keep) * DKW; };
+  auto sub_lo = [&](int n) { return n < n_keep ? 0 : lo_main; };
+  auto sub_hi = [&](int n) { return n < n_keep ? keep_end : hi; };
   const int my_n = (n_sub - warp + NWARPS - 1) / NWARPS;        // this warp's share: sub-tiles warp, warp+NWARPS, ...
   constexpr int stage_elems = (SHARED ? 1 : 2) * DKW * LDS;     // keys that are the values too need no second sub-tile
   bf16* myKV = KVs + (size_t)warp * DSTAGES * stage_elems;
 #pragma unroll
   for (int s = 0; s < DSTAGES - 1; ++s) {
-    if (s < my_n) load_kv_subtile<SHARED>(p, bt, bt_first, hk, k_first + (warp + NWARPS * s) * DKW, lo, hi, same_page, myKV + s * stage_elems,
-                                  myKV + s * stage_elems + DKW * LDS, lane);
+    if (s < my_n) load_kv_subtile<SHARED>(p, bt, bt_first, hk, sub_first(warp + NWARPS * s), sub_lo(warp + NWARPS * s), sub_hi(warp + NWARPS * s),
+                                          same_page, myKV + s * stage_elems, myKV + s * stage_elems + DKW * LDS, lane);
     cp_async_commit();
   }
   uint32_t qf[DQ_IN_REGS ? D / 16 : 1][4];
@@ -634,7 +655,8 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_deep_kernel(const Param
       const int nx = it + DSTAGES - 1;
       if (nx < my_n) {
         bf16* Kn = myKV + (nx % DSTAGES) * stage_elems;
-        load_kv_subtile<SHARED>(p, bt, bt_first, hk, k_first + (warp + NWARPS * nx) * DKW, lo, hi, same_page, Kn, Kn + DKW * LDS, lane);
+        load_kv_subtile<SHARED>(p, bt, bt_first, hk, sub_first(warp + NWARPS * nx), sub_lo(warp + NWARPS * nx), sub_hi(warp + NWARPS * nx),
+                                same_page, Kn, Kn + DKW * LDS, lane);
       }
       cp_async_commit();
       cp_async_wait<DSTAGES - 1>();
@@ -642,7 +664,8 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_deep_kernel(const Param
     __syncwarp();
     const bf16* Ks = myKV + (it % DSTAGES) * stage_elems;
     const bf16* Vs = SHARED ? Ks : Ks + DKW * LDS;
-    const int kbase = k_first + (warp + NWARPS * it) * DKW;
+    const int kbase = sub_first(warp + NWARPS * it);
+    const int t_lo = sub_lo(warp + NWARPS * it), t_hi = sub_hi(warp + NWARPS * it);
     float s[DNT][4];
 #pragma unroll
     for (int j = 0; j < DNT; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
@@ -663,7 +686,7 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_deep_kernel(const Param
       }
     }
     // (rows beyond M hold zero queries; what they compute is finite and never stored)
-    const bool unmasked = kbase >= free_lo && kbase + DKW <= free_hi;
+    const bool unmasked = kbase >= k_first && kbase >= free_lo && kbase + DKW <= free_hi;
     float mx_a = -INFINITY, mx_b = -INFINITY;
     if (unmasked) {
 #pragma unroll
@@ -688,12 +711,12 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_deep_kernel(const Param
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
           const int key = kbase + j * 8 + tq * 2 + e;
-          const bool in_range = key >= lo && key < hi;
-          const bool ok_a = in_range && key <= pos_a && key >= first_a && (p.window <= 0 || key > pos_a - p.window);
+          const bool in_range = key >= t_lo && key < t_hi;
+          const bool ok_a = in_range && key <= pos_a && key >= first_a && (p.window <= 0 || key > pos_a - p.window || key < keep);
           s[j][e] = ok_a ? s[j][e] * p.scale_log2 - slope_a * (float)(pos_a - key) : -INFINITY;
           mx_a = fmaxf(mx_a, s[j][e]);
           if (UPPER) {
-            const bool ok_b = in_range && key <= pos_b && key >= first_b && (p.window <= 0 || key > pos_b - p.window);
+            const bool ok_b = in_range && key <= pos_b && key >= first_b && (p.window <= 0 || key > pos_b - p.window || key < keep);
             s[j][2 + e] = ok_b ? s[j][2 + e] * p.scale_log2 - slope_b * (float)(pos_b - key) : -INFINITY;
             mx_b = fmaxf(mx_b, s[j][2 + e]);
           }
@@ -815,7 +838,7 @@ size_t deep_smem_bytes(int nwarps, bool shared_kv = false) {
 template <bool UPPER, int NWARPS>
 int launch_deep(const Params& p, int n_rows, cudaStream_t stream) {
   const size_t smem = deep_smem_bytes(NWARPS, p.shared_kv != 0);
-  const bool opts = p.slopes != nullptr || p.chunk > 0 || p.cap_over_scale > 0.f || p.sinks != nullptr;
+  const bool opts = p.slopes != nullptr || p.chunk > 0 || p.cap_over_scale > 0.f || p.sinks != nullptr || p.keep_first > 0;
   auto k = p.shared_kv ? (opts ? attention_deep_kernel<UPPER, NWARPS, true, true> : attention_deep_kernel<UPPER, NWARPS, true, false>)
                        : (opts ? attention_deep_kernel<UPPER, NWARPS, false, true> : attention_deep_kernel<UPPER, NWARPS, false, false>);
   if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -850,12 +873,14 @@ SB_EXPORT long long sb_attention_mma_scratch_bytes(int n_rows, int Hkv, int num_
 // ints, zero before the first launch; every launch leaves them zero) or, with tickets == nullptr, in a second kernel.
 // ``slopes`` (float [H] or null) and ``chunk`` (0: none): scores that depend on distance, see Params.
 // ``softcap`` (0: none) and ``sinks`` (float [H] or null): see Params.
-SB_EXPORT int sb_attention_mma_opts(const void* qkv, int q_stride, const void* kc, const void* vc, const int* block_table, int bt_width,
+// ``keep_first`` (0: none): with a window, the keys below it stay visible to every later query.
+SB_EXPORT int sb_attention_mma_keep(const void* qkv, int q_stride, const void* kc, const void* vc, const int* block_table, int bt_width,
                                     const int* cu_q, const int* kv_len, int H, int Hkv, int ps, int num_pages, float scale, int window,
                                     void* out, int n_rows, int max_q, int which, int longest, int num_splits, void* scratch,
                                     int* tickets, const int* wide_rows, int n_wide, const float* slopes, int chunk, float softcap,
-                                    const float* sinks, int kv_div, cudaStream_t stream) {
+                                    const float* sinks, int kv_div, int keep_first, cudaStream_t stream) {
   if (n_rows <= 0 || max_q <= 0) return 0;
+  if (keep_first < 0 || (keep_first > 0 && (window <= 0 || chunk > 0))) return SB_ERR_SHAPE;
   if (H <= 0 || Hkv <= 0 || H % Hkv || ps <= 0 || bt_width <= 0) return SB_ERR_SHAPE;
   // Hkv counts the groups of query heads; the cache has Hkv / kv_div heads (kv_div 1: the usual case)
   if (kv_div < 1 || Hkv % kv_div || (kv_div > 1 && kc != vc)) return SB_ERR_SHAPE;
@@ -867,7 +892,7 @@ SB_EXPORT int sb_attention_mma_opts(const void* qkv, int q_stride, const void* k
   p.block_table = block_table; p.bt_width = bt_width; p.cu_q = cu_q; p.kv_len = kv_len;
   p.H = H; p.Hkv = Hkv; p.G = H / Hkv; p.ps = ps; p.num_pages = num_pages;
   p.ps_shift = (ps & (ps - 1)) == 0 ? __builtin_ctz((unsigned)ps) : -1;
-  p.scale_log2 = scale * LOG2E; p.window = window; p.out = (bf16*)out; p.slopes = slopes; p.chunk = chunk;
+  p.scale_log2 = scale * LOG2E; p.window = window; p.keep_first = keep_first; p.out = (bf16*)out; p.slopes = slopes; p.chunk = chunk;
   p.cap_over_scale = softcap > 0.f ? softcap / scale : 0.f; p.softcap_in = softcap > 0.f ? scale / softcap : 0.f; p.sinks = sinks; p.shared_kv = (kc == vc) ? 1 : 0;
   p.split_size = 0; p.num_splits = num_splits; p.part_o = nullptr; p.part_ml = nullptr; p.tickets = nullptr;
   p.wide_rows = wide_rows; p.heads_in_x = 0;
@@ -943,6 +968,16 @@ SB_EXPORT int sb_attention_mma_opts(const void* qkv, int q_stride, const void* k
   return 0;
 }
 
+SB_EXPORT int sb_attention_mma_opts(const void* qkv, int q_stride, const void* kc, const void* vc, const int* block_table, int bt_width,
+                                    const int* cu_q, const int* kv_len, int H, int Hkv, int ps, int num_pages, float scale, int window,
+                                    void* out, int n_rows, int max_q, int which, int longest, int num_splits, void* scratch,
+                                    int* tickets, const int* wide_rows, int n_wide, const float* slopes, int chunk, float softcap,
+                                    const float* sinks, int kv_div, cudaStream_t stream) {
+  return sb_attention_mma_keep(qkv, q_stride, kc, vc, block_table, bt_width, cu_q, kv_len, H, Hkv, ps, num_pages, scale, window, out,
+                               n_rows, max_q, which, longest, num_splits, scratch, tickets, wide_rows, n_wide, slopes, chunk, softcap,
+                               sinks, kv_div, 0, stream);
+}
+
 // ---------------------------------------------------------------------------------------------------------
 // Decoding attention with built-in scratch memory, for callers that must not allocate (attention_noalloc.h).
 #include "attention_noalloc.h"
@@ -1008,7 +1043,7 @@ SB_EXPORT int sb_attention_decode_noalloc(const void* qkv, int q_stride, const v
   p.block_table = block_table; p.bt_width = bt_width; p.cu_q = cu_q; p.kv_len = kv_len;
   p.H = H; p.Hkv = Hkv; p.G = G; p.ps = ps; p.num_pages = num_pages;
   p.ps_shift = (ps & (ps - 1)) == 0 ? __builtin_ctz((unsigned)ps) : -1;
-  p.scale_log2 = scale * LOG2E; p.window = window; p.out = (bf16*)out; p.slopes = nullptr; p.chunk = 0;
+  p.scale_log2 = scale * LOG2E; p.window = window; p.keep_first = 0; p.out = (bf16*)out; p.slopes = nullptr; p.chunk = 0;
   p.cap_over_scale = 0.f; p.softcap_in = 0.f; p.sinks = nullptr; p.shared_kv = (kc == vc) ? 1 : 0; p.cache_Hkv = Hkv; p.kv_div = 1;
   p.split_size = 0; p.num_splits = num_splits; p.part_o = nullptr; p.part_ml = nullptr; p.tickets = nullptr;
   p.wide_rows = nullptr;

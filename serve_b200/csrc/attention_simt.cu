@@ -38,7 +38,7 @@ __global__ void __launch_bounds__(THREADS) attention_simt_kernel(
     const T* __restrict__ qkv, int q_stride, const T* __restrict__ kc, const T* __restrict__ vc,  // caches [P, Hkv, ps, D]
     const int* __restrict__ block_table, int bt_width, const int* __restrict__ cu_q, const int* __restrict__ kv_len, int H,
     int Hkv, int ps, int num_pages, float scale, int window, T* __restrict__ out, int decode_apart,
-    const float* __restrict__ slopes, int chunk, float softcap, const float* __restrict__ sinks) {
+    const float* __restrict__ slopes, int chunk, float softcap, const float* __restrict__ sinks, int keep) {
   extern __shared__ float smem[];
   float* Qs = smem;                 // [BM][D]
   float* Ks = Qs + BM * D;          // [BN][KSTRIDE]
@@ -76,13 +76,16 @@ __global__ void __launch_bounds__(THREADS) attention_simt_kernel(
   for (int c = 0; c < D / 8; ++c) acc[c] = 0.f;
 
   const int* bt = block_table + (size_t)r * bt_width;
-  for (int kt = (lo / BN) * BN; kt < hi; kt += BN) {
+  // keys below ``keep`` stay visible behind the window: the tiles that hold those before the window's first tile come first
+  const int keep_end = min(keep, lo), lo_tile = (lo / BN) * BN;
+  for (int kt = keep_end > 0 ? 0 : lo_tile; kt < hi; kt += BN) {
+    if (kt >= keep_end && kt < lo_tile) kt = lo_tile;      // nothing to read between the kept keys and the window
     __syncthreads();  // previous tile fully consumed (and Qs written, first time round)
     for (int w = tid; w < BN * D; w += THREADS) {
       const int kj = w / D, d = w - kj * D;
       const int key = kt + kj;
       float kvv = 0.f, vvv = 0.f;
-      if (key >= lo && key < hi) {
+      if ((key >= lo || key < keep_end) && key < hi) {
         const int blk = key / ps;
         const int page = blk < bt_width ? bt[blk] : -1;
         if (page >= 0 && page < num_pages) {
@@ -108,7 +111,7 @@ __global__ void __launch_bounds__(THREADS) attention_simt_kernel(
 #pragma unroll
     for (int c = 0; c < BN / 8; ++c) {
       const int key = kt + jj + 8 * c;
-      const bool ok = row_ok && key <= pi && key >= chunk_lo && (window <= 0 || key > pi - window);
+      const bool ok = row_ok && key <= pi && key >= chunk_lo && (window <= 0 || key > pi - window || key < keep);
       float sv = s[c] * scale;
       if (softcap > 0.f) sv = softcap * tanhf(sv / softcap);
       s[c] = ok ? sv - slope * (float)(pi - key) : -INFINITY;
@@ -200,7 +203,7 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_simt_decode_kernel(
     const T* __restrict__ qkv, int q_stride, const T* __restrict__ kc, const T* __restrict__ vc,
     const int* __restrict__ block_table, int bt_width, const int* __restrict__ cu_q, const int* __restrict__ kv_len, int H,
     int Hkv, int ps, int num_pages, float scale, int window, T* __restrict__ out, const float* __restrict__ slopes, int chunk,
-    float softcap, const float* __restrict__ sinks) {
+    float softcap, const float* __restrict__ sinks, int keep) {
   extern __shared__ float smem[];
   float* Qs = smem;                                        // [16][D]
   float* Om = Qs + 16 * D;                                 // [DEC_STREAMS][DEC_ROWS][LPK * EPL]
@@ -253,19 +256,25 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_simt_decode_kernel(
       off = (((size_t)page * Hkv + hk) * ps + (key - blk * ps)) * D;
       return true;
     };
+    // The keys a stream walks are numbered without the gap between the kept first keys and the window: number n is key
+    // n below keep_end and key n - keep_end + lo from there on.
+    const int keep_end = min(keep, lo);
+    auto key_of = [&](int n) { return n < keep_end ? n : n - keep_end + lo; };
     float kn[EPL], vn[EPL];
     size_t off = 0;
-    int key = lo + stream;
+    int number = stream;
+    int key = key_of(number);
     bool there = locate(key, off);
     dec_load(kc, off, sub, there, kn);
     dec_load(vc, off, sub, there, vn);
-    for (int base = lo; base < hi; base += DEC_STREAMS) {
+    for (int base = lo - keep_end; base < hi; base += DEC_STREAMS) {
       float kv[EPL], vv[EPL];
 #pragma unroll
       for (int e = 0; e < EPL; ++e) { kv[e] = kn[e]; vv[e] = vn[e]; }
       const int this_key = key;
       const bool this_there = there;
-      key += DEC_STREAMS;
+      number += DEC_STREAMS;
+      key = key_of(number);
       there = locate(key, off);
       dec_load(kc, off, sub, there, kn);
       dec_load(vc, off, sub, there, vn);
@@ -276,7 +285,8 @@ __global__ void __launch_bounds__(DEC_WARPS * 32) attention_simt_decode_kernel(
         for (int e = 0; e < EPL; ++e) sc += q[i][e] * kv[e];
 #pragma unroll
         for (int o = LPK / 2; o > 0; o >>= 1) sc += __shfl_xor_sync(0xffffffffu, sc, o);
-        const bool ok = this_there && this_key <= pos[i] && this_key >= first_key[i] && (window <= 0 || this_key > pos[i] - window);
+        const bool ok = this_there && this_key <= pos[i] && this_key >= first_key[i] &&
+                        (window <= 0 || this_key > pos[i] - window || this_key < keep);
         if (ok) {
           if (softcap > 0.f) sc = softcap * tanhf(sc / softcap);
           sc -= slope[i] * (float)(pos[i] - this_key);
@@ -327,11 +337,13 @@ SB_EXPORT int sb_attention_simt_head_dim() { return D; }
 
 // As sb_attention_simt below, with every option: ``slopes`` (float [H] or null), ``chunk`` (0: none), ``softcap`` (0: none)
 // and ``sinks`` (float [H] or null).
-SB_EXPORT int sb_attention_simt_opts(const void* qkv, int q_stride, const void* kc, const void* vc, const int* block_table,
+// and ``keep`` (0: none; with a window: the keys below it stay visible to every later query).
+SB_EXPORT int sb_attention_simt_keep(const void* qkv, int q_stride, const void* kc, const void* vc, const int* block_table,
                                      int bt_width, const int* cu_q, const int* kv_len, int H, int Hkv, int ps, int num_pages,
                                      float scale, int window, void* out, int n_rows, int max_q, int dtype, const float* slopes,
-                                     int chunk, float softcap, const float* sinks, cudaStream_t stream) {
+                                     int chunk, float softcap, const float* sinks, int keep, cudaStream_t stream) {
   if (n_rows <= 0 || max_q <= 0) return 0;
+  if (keep < 0 || (keep > 0 && (window <= 0 || chunk > 0))) return SB_ERR_SHAPE;
   if (H <= 0 || Hkv <= 0 || H % Hkv || ps <= 0 || bt_width <= 0) return SB_ERR_SHAPE;
   if (H > 65535 || n_rows > 65535) return SB_ERR_LIMIT;
   const size_t smem = (size_t)(BM * D + BN * KSTRIDE + BN * D + BM * BN) * sizeof(float);
@@ -348,7 +360,7 @@ SB_EXPORT int sb_attention_simt_opts(const void* qkv, int q_stride, const void* 
       auto k = attention_simt_kernel<float>;
       if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       k<<<grid, THREADS, smem, stream>>>((const float*)qkv, q_stride, (const float*)kc, (const float*)vc, block_table, bt_width, cu_q,
-                                         kv_len, H, Hkv, ps, num_pages, scale, window, (float*)out, decode_shape ? 1 : 0, slopes, chunk, softcap, sinks);
+                                         kv_len, H, Hkv, ps, num_pages, scale, window, (float*)out, decode_shape ? 1 : 0, slopes, chunk, softcap, sinks, keep);
       SB_LAUNCH_CHECK();
     }
     if (decode_shape) {
@@ -358,14 +370,14 @@ SB_EXPORT int sb_attention_simt_opts(const void* qkv, int q_stride, const void* 
     if (decode_shape)
       attention_simt_decode_kernel<float><<<dgrid, DEC_WARPS * 32, dsmem, stream>>>(
           (const float*)qkv, q_stride, (const float*)kc, (const float*)vc, block_table, bt_width, cu_q, kv_len, H, Hkv, ps, num_pages,
-          scale, window, (float*)out, slopes, chunk, softcap, sinks);
+          scale, window, (float*)out, slopes, chunk, softcap, sinks, keep);
   } else if (dtype == SB_DTYPE_BF16) {
     if (tiles_needed) {
       auto k = attention_simt_kernel<__nv_bfloat16>;
       if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
       k<<<grid, THREADS, smem, stream>>>((const __nv_bfloat16*)qkv, q_stride, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc,
                                          block_table, bt_width, cu_q, kv_len, H, Hkv, ps, num_pages, scale, window,
-                                         (__nv_bfloat16*)out, decode_shape ? 1 : 0, slopes, chunk, softcap, sinks);
+                                         (__nv_bfloat16*)out, decode_shape ? 1 : 0, slopes, chunk, softcap, sinks, keep);
       SB_LAUNCH_CHECK();
     }
     if (decode_shape) {
@@ -375,12 +387,20 @@ SB_EXPORT int sb_attention_simt_opts(const void* qkv, int q_stride, const void* 
     if (decode_shape)
       attention_simt_decode_kernel<__nv_bfloat16><<<dgrid, DEC_WARPS * 32, dsmem, stream>>>(
           (const __nv_bfloat16*)qkv, q_stride, (const __nv_bfloat16*)kc, (const __nv_bfloat16*)vc, block_table, bt_width, cu_q, kv_len, H,
-          Hkv, ps, num_pages, scale, window, (__nv_bfloat16*)out, slopes, chunk, softcap, sinks);
+          Hkv, ps, num_pages, scale, window, (__nv_bfloat16*)out, slopes, chunk, softcap, sinks, keep);
   } else {
     return SB_ERR_DTYPE;
   }
   SB_LAUNCH_CHECK();
   return 0;
+}
+
+SB_EXPORT int sb_attention_simt_opts(const void* qkv, int q_stride, const void* kc, const void* vc, const int* block_table,
+                                     int bt_width, const int* cu_q, const int* kv_len, int H, int Hkv, int ps, int num_pages,
+                                     float scale, int window, void* out, int n_rows, int max_q, int dtype, const float* slopes,
+                                     int chunk, float softcap, const float* sinks, cudaStream_t stream) {
+  return sb_attention_simt_keep(qkv, q_stride, kc, vc, block_table, bt_width, cu_q, kv_len, H, Hkv, ps, num_pages, scale, window, out,
+                                n_rows, max_q, dtype, slopes, chunk, softcap, sinks, 0, stream);
 }
 
 // The two options of scores that depend on distance only.

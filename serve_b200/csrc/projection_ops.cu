@@ -271,7 +271,201 @@ __global__ void gated_activation_bf16_vec_kernel(const __nv_bfloat16* __restrict
   }
 }
 
+// ------------------------------------------------------------------------------------------------ dynamic tanh
+// A norm without statistics: y = tanh(alpha * x) * w + b, every element on its own; par = [w (dim) | b (dim) | alpha].
+//   x given:  v = x[row] (+ d), d = delta[row] or, with ``through`` (the parameters of the norm the delta still has to
+//             pass), tanh(alpha' delta[row]) w' + b'; x[row] = v unless rows are picked; out = dyt(v)
+//   x null:   out = dyt(delta)
+// Float arithmetic throughout; delta and out have dtypes of their own.
+template <typename TD, typename TO>
+__global__ void __launch_bounds__(256) dynamic_tanh_kernel(float* __restrict__ x, const TD* __restrict__ delta, const float* __restrict__ through,
+                                                           const int* __restrict__ rows, const float* __restrict__ par, TO* __restrict__ out,
+                                                           int n_rows, int dim) {
+  const float alpha = par[2 * dim];
+  const float alpha_d = through ? through[2 * dim] : 0.f;
+  const size_t total = (size_t)n_rows * dim;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int r = (int)(i / dim), c = (int)(i - (size_t)r * dim);
+    const size_t src = (size_t)(rows ? rows[r] : r) * dim + c;
+    float v;
+    if (x) {
+      v = x[src];
+      if (delta) {
+        float d = to_float(delta[src]);
+        if (through) d = tanhf(alpha_d * d) * through[c] + through[dim + c];
+        v += d;
+        if (!rows) x[src] = v;
+      }
+    } else {
+      v = to_float(delta[src]);
+    }
+    out[i] = from_float<TO>(tanhf(alpha * v) * par[c] + par[dim + c]);
+  }
+}
+
+// ------------------------------------------------------------------------------------- activations, bias, on their own
+constexpr int ACT_RELU_SQUARED = 0, ACT_GELU_TANH = 1, ACT_SILU = 2, ACT_TANH = 3;
+
+__device__ __forceinline__ float activate(float z, int kind) {
+  if (kind == ACT_RELU_SQUARED) { const float r = fmaxf(z, 0.f); return r * r; }
+  if (kind == ACT_GELU_TANH) return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+  if (kind == ACT_SILU) return z / (1.f + expf(-z));
+  return kind == ACT_TANH ? tanhf(z) : z;
+}
+
+// out = act(x [+ bias per column]), computed in float, rounded once; x and out may be the same buffer.
+template <typename T>
+__global__ void __launch_bounds__(256) activation_kernel(const T* x, const float* __restrict__ bias, T* out, size_t total, int cols, int kind) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    float z = to_float(x[i]);
+    if (bias) z += bias[i % cols];
+    out[i] = from_float<T>(activate(z, kind));
+  }
+}
+
+__global__ void __launch_bounds__(256) add_bias_kernel(float* __restrict__ x, const float* __restrict__ bias, size_t total, int cols) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) x[i] += bias[i % cols];
+}
+
+// ------------------------------------------------------------- bias, whole-projection norm, partial rotation, cache write
+// sums float [T, (H + 2 G) * D] (row stride given): the float sums of the fused query | key | value projection, heads padded
+// to D with zeros (G = 0: queries only). Per token, one block: add the bias; divide all queries together (and all keys
+// together) by the root mean square over their H * dim (G * dim) true elements and multiply by a float weight laid out
+// like the padded projection; rotate the first ``rot`` elements of every query and key head, element i with i + rot / 2,
+// by the angle position * inv_freq[i]; queries to q_out [T, H * D], keys and values to their page. Everything is float
+// until the one rounding at the store.
+template <typename T>
+__global__ void __launch_bounds__(256) qk_prepare_kernel(
+    const float* __restrict__ sums, int stride, const float* __restrict__ bias, const int* __restrict__ positions,
+    const int* __restrict__ token_row, int H, int G, int D, int dim, const float* __restrict__ q_weight, const float* __restrict__ k_weight,
+    float eps, const float* __restrict__ inv_freq, int rot, T* __restrict__ q_out, int q_stride, T* __restrict__ kc, T* __restrict__ vc,
+    const int* __restrict__ block_table, int bt_width, int ps, int num_pages, int* __restrict__ errors) {
+  __shared__ float red[32];
+  const int t = blockIdx.x;
+  const float* row = sums + (size_t)t * stride;
+  const int nq = H * D, nk = G * D, half = rot >> 1;
+  const int pos = positions[t];
+  auto val = [&](int i) { return row[i] + (bias ? bias[i] : 0.f); };
+  float inv_q = 1.f, inv_k = 1.f;
+  if (q_weight != nullptr) {
+    float sq = 0.f;
+    for (int i = threadIdx.x; i < nq; i += blockDim.x) { const float v = val(i); sq += v * v; }
+    inv_q = 1.0f / sqrtf(block_sum(sq, red) / (float)(H * dim) + eps);
+  }
+  if (k_weight != nullptr && G > 0) {
+    float sk = 0.f;
+    for (int i = threadIdx.x; i < nk; i += blockDim.x) { const float v = val(nq + i); sk += v * v; }
+    inv_k = 1.0f / sqrtf(block_sum(sk, red) / (float)(G * dim) + eps);
+  }
+  // element d of a head that starts at column ``base``, normalised and rotated
+  auto prepared = [&](int base, int w_base, int d, float inv, const float* w) {
+    auto normed = [&](int e) { const float v = val(base + e); return w ? v * inv * w[w_base + e] : v; };
+    const float v = normed(d);
+    if (d >= rot) return v;
+    const int j = d < half ? d : d - half;
+    float sn, cs;
+    sincosf((float)pos * inv_freq[j], &sn, &cs);
+    const float other = normed(d < half ? d + half : d - half);
+    return d < half ? v * cs - other * sn : v * cs + other * sn;
+  };
+  for (int i = threadIdx.x; i < nq; i += blockDim.x) {
+    const int h = i / D, d = i - h * D;
+    q_out[(size_t)t * q_stride + i] = from_float<T>(prepared(h * D, h * D, d, inv_q, q_weight));
+  }
+  if (G == 0) return;
+  const int blk = pos / ps;
+  const int page = (pos >= 0 && blk < bt_width) ? block_table[(size_t)token_row[t] * bt_width + blk] : -1;
+  if (page < 0 || page >= num_pages) {
+    if (threadIdx.x == 0) atomicAdd(errors, 1);
+    return;
+  }
+  const int within = pos - blk * ps;
+  for (int i = threadIdx.x; i < nk; i += blockDim.x) {
+    const int g = i / D, d = i - g * D;
+    const size_t off = (((size_t)page * G + g) * ps + within) * D + d;
+    kc[off] = from_float<T>(prepared(nq + g * D, g * D, d, inv_k, k_weight));
+    vc[off] = from_float<T>(val(nq + nk + i));
+  }
+}
+
 }  // namespace
+
+template <typename TD, typename TO>
+static int launch_dynamic_tanh(float* x, const void* delta, const float* through, const int* rows, const float* par, void* out, int n_rows,
+                               int dim, cudaStream_t stream) {
+  const size_t total = (size_t)n_rows * dim, want = (total + 255) / 256;
+  const int blocks = (int)(want < (size_t)sm_count() * 16 ? want : (size_t)sm_count() * 16);
+  dynamic_tanh_kernel<TD, TO><<<blocks, 256, 0, stream>>>(x, (const TD*)delta, through, rows, par, (TO*)out, n_rows, dim);
+  SB_LAUNCH_CHECK();
+  return 0;
+}
+
+// x float [*, dim] or null; delta [*, dim] of delta_dtype or null; through, par float [2 dim + 1]; rows int [n_rows] or null;
+// out [n_rows, dim] of out_dtype.
+SB_EXPORT int sb_add_dynamic_tanh(float* x, const void* delta, int delta_dtype, const float* through, const int* rows, const float* par,
+                                  void* out, int out_dtype, int n_rows, int dim, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (dim <= 0 || !par || !out || (!x && !delta)) return SB_ERR_SHAPE;
+  const bool df = delta == nullptr || delta_dtype == SB_DTYPE_F32;
+  if (!df && delta_dtype != SB_DTYPE_BF16) return SB_ERR_DTYPE;
+  if (out_dtype == SB_DTYPE_F32)
+    return df ? launch_dynamic_tanh<float, float>(x, delta, through, rows, par, out, n_rows, dim, stream)
+              : launch_dynamic_tanh<__nv_bfloat16, float>(x, delta, through, rows, par, out, n_rows, dim, stream);
+  if (out_dtype == SB_DTYPE_BF16)
+    return df ? launch_dynamic_tanh<float, __nv_bfloat16>(x, delta, through, rows, par, out, n_rows, dim, stream)
+              : launch_dynamic_tanh<__nv_bfloat16, __nv_bfloat16>(x, delta, through, rows, par, out, n_rows, dim, stream);
+  return SB_ERR_DTYPE;
+}
+
+// out = act(x + bias): x, out [n_rows, cols] (contiguous, may be the same buffer), bias float [cols] or null.
+// kind: 0 relu squared, 1 gelu (tanh form), 2 silu, 3 tanh.
+SB_EXPORT int sb_activation(const void* x, const float* bias, void* out, int n_rows, int cols, int kind, int dtype, cudaStream_t stream) {
+  if (n_rows <= 0 || cols <= 0) return 0;
+  if (kind < 0 || kind > 3) return SB_ERR_SHAPE;
+  const size_t total = (size_t)n_rows * cols, want = (total + 255) / 256;
+  const int blocks = (int)(want < (size_t)sm_count() * 16 ? want : (size_t)sm_count() * 16);
+  if (dtype == SB_DTYPE_F32)
+    activation_kernel<float><<<blocks, 256, 0, stream>>>((const float*)x, bias, (float*)out, total, cols, kind);
+  else if (dtype == SB_DTYPE_BF16)
+    activation_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)x, bias, (__nv_bfloat16*)out, total, cols, kind);
+  else
+    return SB_ERR_DTYPE;
+  SB_LAUNCH_CHECK();
+  return 0;
+}
+
+SB_EXPORT int sb_add_bias(float* x, const float* bias, int n_rows, int cols, cudaStream_t stream) {
+  if (n_rows <= 0 || cols <= 0) return 0;
+  const size_t total = (size_t)n_rows * cols, want = (total + 255) / 256;
+  const int blocks = (int)(want < (size_t)sm_count() * 16 ? want : (size_t)sm_count() * 16);
+  add_bias_kernel<<<blocks, 256, 0, stream>>>(x, bias, total, cols);
+  SB_LAUNCH_CHECK();
+  return 0;
+}
+
+// bias float [(H + 2 G) * D] or null; q_weight float [H * D], k_weight float [G * D] or null (no norm of that side);
+// inv_freq float [>= rot / 2]; G = 0 writes no cache.
+SB_EXPORT int sb_qk_prepare(const float* sums, int stride, const float* bias, const int* positions, const int* token_row, int H, int G, int D,
+                            int dim, const float* q_weight, const float* k_weight, float eps, const float* inv_freq, int rot, void* q_out,
+                            int q_stride, void* kc, void* vc, const int* block_table, int bt_width, int ps, int num_pages, int* errors,
+                            int n_tokens, int dtype, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (H <= 0 || G < 0 || D <= 0 || dim <= 0 || dim > D || stride < (H + 2 * G) * D || q_stride < H * D) return SB_ERR_SHAPE;
+  if (rot < 0 || (rot & 1) || rot > dim || (rot > 0 && !inv_freq)) return SB_ERR_SHAPE;
+  if (G > 0 && (ps <= 0 || bt_width <= 0 || !kc || !vc || !errors)) return SB_ERR_SHAPE;
+  if (dtype == SB_DTYPE_F32)
+    qk_prepare_kernel<float><<<n_tokens, 256, 0, stream>>>(sums, stride, bias, positions, token_row, H, G, D, dim, q_weight, k_weight, eps,
+                                                            inv_freq, rot, (float*)q_out, q_stride, (float*)kc, (float*)vc, block_table,
+                                                            bt_width, ps, num_pages, errors);
+  else if (dtype == SB_DTYPE_BF16)
+    qk_prepare_kernel<__nv_bfloat16><<<n_tokens, 256, 0, stream>>>(sums, stride, bias, positions, token_row, H, G, D, dim, q_weight, k_weight,
+                                                                    eps, inv_freq, rot, (__nv_bfloat16*)q_out, q_stride, (__nv_bfloat16*)kc,
+                                                                    (__nv_bfloat16*)vc, block_table, bt_width, ps, num_pages, errors);
+  else
+    return SB_ERR_DTYPE;
+  SB_LAUNCH_CHECK();
+  return 0;
+}
 
 SB_EXPORT int sb_add_layernorm(float* x, const void* delta, const int* rows, const void* weight, int weight_dtype, void* out, int n_rows,
                                int dim, float eps, int dtype, cudaStream_t stream) {

@@ -85,6 +85,77 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
   }
 }
 
+// As moe_route_kernel, for a router with a bias on the choice: the scores (softmax over the first E of a row's ``stride``
+// logits, or sigmoid) choose through score + bias[e], lowest index first on ties, while the weights are the scores
+// themselves, divided by (their sum + sum_eps) if asked. E counts every output the router scores; an index at or beyond
+// the number of real experts means "the token itself" to the kernels after this one.
+__global__ void __launch_bounds__(128) moe_route_bias_kernel(const float* __restrict__ logits, int stride, int E, int top, int score_kind,
+                                                             int renorm, float sum_eps, const float* __restrict__ bias, int n_tokens,
+                                                             int* __restrict__ idx, float* __restrict__ wts) {
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (t >= n_tokens) return;
+  const float* z = logits + (size_t)t * stride;
+  float score[ROUTE_PER_LANE], pick[ROUTE_PER_LANE];
+  float zmax = -INFINITY;
+#pragma unroll
+  for (int u = 0; u < ROUTE_PER_LANE; ++u) {
+    const int e = lane + 32 * u;
+    score[u] = e < E ? z[e] : -INFINITY;
+    zmax = fmaxf(zmax, score[u]);
+  }
+  if (score_kind == 1) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) zmax = fmaxf(zmax, __shfl_xor_sync(0xffffffffu, zmax, o));
+    float part = 0.f;
+#pragma unroll
+    for (int u = 0; u < ROUTE_PER_LANE; ++u)
+      if (lane + 32 * u < E) { score[u] = expf(score[u] - zmax); part += score[u]; }
+    const float denom = warp_sum(part);
+#pragma unroll
+    for (int u = 0; u < ROUTE_PER_LANE; ++u)
+      if (lane + 32 * u < E) score[u] /= denom;
+  } else {
+#pragma unroll
+    for (int u = 0; u < ROUTE_PER_LANE; ++u)
+      if (lane + 32 * u < E) score[u] = sigmoid_f(score[u]);
+  }
+#pragma unroll
+  for (int u = 0; u < ROUTE_PER_LANE; ++u) {
+    const int e = lane + 32 * u;
+    pick[u] = e < E ? score[u] + (bias ? bias[e] : 0.f) : -INFINITY;
+  }
+  float val = 0.f, total = 0.f;                 // lane s keeps the s-th choice
+  int chosen = 0;
+  for (int s = 0; s < top; ++s) {
+    float m = -INFINITY, sc = 0.f;
+    int arg = 0x7fffffff;
+#pragma unroll
+    for (int u = 0; u < ROUTE_PER_LANE; ++u) {
+      const int e = lane + 32 * u;
+      if (e < E && pick[u] != -INFINITY && (pick[u] > m || (pick[u] == m && e < arg))) { m = pick[u]; arg = e; sc = score[u]; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float om = __shfl_xor_sync(0xffffffffu, m, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, arg, o);
+      const float os = __shfl_xor_sync(0xffffffffu, sc, o);
+      if (om > m || (om == m && oa < arg)) { m = om; arg = oa; sc = os; }
+    }
+    if (arg != 0x7fffffff && (arg & 31) == lane) {
+#pragma unroll
+      for (int u = 0; u < ROUTE_PER_LANE; ++u)
+        if (u == (arg >> 5)) pick[u] = -INFINITY;    // taken
+    }
+    total += sc;
+    if (lane == s) { val = sc; chosen = arg == 0x7fffffff ? 0 : arg; }
+  }
+  if (lane < top) {
+    idx[(size_t)t * top + lane] = chosen;
+    wts[(size_t)t * top + lane] = renorm ? val / (total + sum_eps) : val;
+  }
+}
+
 constexpr int TM = 32;            // rows of a tile of the plain-arithmetic products (the tensor-core ones take MB_M)
 
 // One block. order[offsets[e] .. offsets[e+1]) = the pairs of expert e; tiles: (expert, first row) for every TM rows
@@ -524,6 +595,31 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restric
   }
 }
 
+
+// The sum over a token's choices when some of them are not experts, plus what every token gets:
+//   out[t] = sum_k ( idx[t, k] < E_real ? parts[t * top + k] : wts[t * top + k] * x[t] )  +  g_t * shared[t]
+// with g_t = sigmoid(gate[t * gate_stride]) if a gate is given, else 1; shared may be null.
+template <typename T>
+__global__ void __launch_bounds__(256) moe_combine_more_kernel(const float* __restrict__ parts, const int* __restrict__ idx,
+                                                               const float* __restrict__ wts, int E_real, const T* __restrict__ x,
+                                                               int x_stride, const T* __restrict__ shared, const float* __restrict__ gate,
+                                                               int gate_stride, int top, int N, long long total, T* __restrict__ out) {
+  for (long long w = (long long)blockIdx.x * blockDim.x + threadIdx.x; w < total; w += (long long)gridDim.x * blockDim.x) {
+    const long long t = w / N;
+    const int c = (int)(w - t * N);
+    float s = 0.f;
+    for (int k = 0; k < top; ++k) {
+      const size_t pair = (size_t)t * top + k;
+      s += idx[pair] < E_real ? parts[pair * N + c] : wts[pair] * to_float(x[(size_t)t * x_stride + c]);
+    }
+    if (shared) {
+      const float g = gate ? sigmoid_f(gate[(size_t)t * gate_stride]) : 1.f;
+      s += g * to_float(shared[w]);
+    }
+    out[w] = from_float<T>(s);
+  }
+}
+
 }  // namespace
 
 // Rows of a tile for a step's products: the tensor-core kernels (bfloat16, k a multiple of 32 and rows 16-byte aligned on
@@ -679,6 +775,41 @@ SB_EXPORT int sb_moe_combine(const float* parts, int top, int n_tokens, int N, v
   const int blocks = (int)(want < sm_count() * 8 ? want : sm_count() * 8);
   if (dtype == SB_DTYPE_F32) moe_combine_kernel<float><<<blocks, 256, 0, stream>>>(parts, top, N, total, (float*)out);
   else if (dtype == SB_DTYPE_BF16) moe_combine_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(parts, top, N, total, (__nv_bfloat16*)out);
+  else return SB_ERR_DTYPE;
+  SB_LAUNCH_CHECK();
+  return 0;
+}
+
+// As sb_moe_route with more: the row stride of the logits (columns beyond E are not the router's), a float bias [E] or
+// null that joins the scores for the choice only, and sum_eps, added to the sum the chosen scores are divided by.
+SB_EXPORT int sb_moe_route_bias(const float* logits, int stride, int E, int top, int score_kind, int renorm, float sum_eps,
+                                const float* bias, int n_tokens, int* idx, float* wts, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (E <= 0 || top <= 0 || top > E || top > ROUTE_MAX_TOP || E > 32 * ROUTE_PER_LANE) return SB_ERR_LIMIT;
+  if (stride < E) return SB_ERR_SHAPE;
+  moe_route_bias_kernel<<<(n_tokens + 3) / 4, 128, 0, stream>>>(logits, stride, E, top, score_kind, renorm, sum_eps, bias, n_tokens, idx, wts);
+  SB_LAUNCH_CHECK();
+  return 0;
+}
+
+// out [T, N] = the sum of a token's rows of parts (float [T * top, N]) where idx names one of the E_real experts, and
+// wts * x[t] where it names none (N must then be x's width); plus shared [T, N] (or null), times sigmoid(gate[t]) if a
+// gate (float, rows gate_stride apart) is given.
+SB_EXPORT int sb_moe_combine_more(const float* parts, const int* idx, const float* wts, int E_real, const void* x, int x_stride,
+                                  const void* shared, const float* gate, int gate_stride, int top, int n_tokens, int N, void* out,
+                                  int dtype, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (!parts || !idx || !wts || !x || top <= 0 || x_stride < N) return SB_ERR_SHAPE;
+  const long long total = (long long)n_tokens * N;
+  const long long want = (total + 255) / 256;
+  const int blocks = (int)(want < sm_count() * 8 ? want : sm_count() * 8);
+  if (dtype == SB_DTYPE_F32)
+    moe_combine_more_kernel<float><<<blocks, 256, 0, stream>>>(parts, idx, wts, E_real, (const float*)x, x_stride, (const float*)shared, gate,
+                                                               gate_stride, top, N, total, (float*)out);
+  else if (dtype == SB_DTYPE_BF16)
+    moe_combine_more_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(parts, idx, wts, E_real, (const __nv_bfloat16*)x, x_stride,
+                                                                       (const __nv_bfloat16*)shared, gate, gate_stride, top, N, total,
+                                                                       (__nv_bfloat16*)out);
   else return SB_ERR_DTYPE;
   SB_LAUNCH_CHECK();
   return 0;

@@ -1,7 +1,8 @@
 // Kernels of mixers that carry a state of fixed size from token to token instead of (or beside) cached keys:
-// short causal convolutions over time, linear recurrences over a matrix state per head (fixed decay, selective
-// state space, gated delta rule), the normalisation-and-gate that follows them, and the cache write of an
-// attention whose values are normalised and whose queries and keys are not rotated.
+// short causal convolutions over time, the blends of a token's input with its predecessor's (token shift), linear
+// recurrences over a matrix state per head (fixed decay, selective state space, gated delta rule, a decay per key
+// channel with a bonus for the current token), the normalisation-and-gate that follows them, and the cache write of
+// an attention whose values are normalised and whose queries and keys are not rotated.
 //
 // A step is ragged: row r brings the tokens cu_q[r] .. cu_q[r+1]-1 and owns state slot slots[r]. State tensors
 // are float [max_slots, ...] and are zero when a slot is handed out, so "zeros before the start" needs no
@@ -145,6 +146,8 @@ __global__ void __launch_bounds__(CONV_THREADS) conv_state_kernel(const T* __res
 //   S <- a * S;   u = v                      (MODE_DECAY, MODE_SSM: u = dt * x)
 //                 u = beta * (v - S^T k)     (MODE_DELTA)
 //   S <- S + k u^T;   o = S^T q  (+ D * x for MODE_SSM)
+// MODE_WKV reads out first: o = S^T q + (sum_i q_i b_i k_i) v with a bonus b per (head, row) for the token's own
+// k v^T; then S <- diag(a) S + k v^T with a decay a = exp(-exp(rate + bias)) per row of S.
 // Two kernels. The first works on every (token, head) at once and leaves, as float, what the walk over the tokens
 // reads: q and k (after silu, or as unit vectors), the decays (after softplus and the exponentials), the values and
 // the per-token factor (dt or beta). The second walks: the columns of S never meet, so a block takes (request, head, a
@@ -154,7 +157,7 @@ __global__ void __launch_bounds__(CONV_THREADS) conv_state_kernel(const T* __res
 // tokens' vectors come through a two-stage cp.async ring, REC_TS tokens a stage, so the next tokens arrive while
 // these are worked on; a thread's rows are 4 P apart in fours, so it reads them 16 bytes at a time and the lanes of
 // a column read neighbouring 16 bytes.
-constexpr int MODE_DECAY = 0, MODE_SSM = 1, MODE_DELTA = 2;
+constexpr int MODE_DECAY = 0, MODE_SSM = 1, MODE_DELTA = 2, MODE_WKV = 3;
 constexpr int REC_RPT = 16;
 constexpr int REC_THREADS = 128;
 constexpr int REC_TS = 16;
@@ -163,7 +166,9 @@ struct RecArgs {
   const void* q; const void* k; const void* v;      // [T, *] activations: row strides below, head h at h * dk (dv)
   int q_stride, k_stride, v_stride;
   const void* aux;  int aux_stride;                  // SSM: dt before softplus [T, H]; DELTA: beta before the sigmoid [T, H]
-  const void* rate; int rate_stride;                 // DELTA: decay rate before softplus [T, H * dk]
+  const void* rate; int rate_stride;                 // DELTA: decay rate before softplus [T, H * dk], or [T, H] with rate_per_head;
+  int rate_dtype, rate_per_head;                     // WKV: the exponent's variable part [T, H * dk] (dt_bias [H * dk] is added)
+  const float* bonus;                                // WKV: [H, dk] float
   const void* decay;                                 // DECAY: [H] float decays
   const void* a_log; const void* dt_bias; const void* d_skip;   // parameters (dtype par_dtype)
   int par_dtype;
@@ -173,7 +178,7 @@ struct RecArgs {
   float* out; int out_stride;                        // [T, H * dv] float
   int H, Hqk, dk, dv, P, dkp, dvp, n_tokens;
   float q_scale;
-  // float work space, made by the first kernel: qf, kf [T, Hqk, dkp]; af [T, H, dkp] (DELTA); vf [T, H, dvp]; sc, dec [T, H]
+  // float work space, made by the first kernel: qf, kf [T, Hqk, dkp]; af [T, H, dkp] (DELTA, WKV); vf [T, H, dvp]; sc, dec [T, H]
   float *qf, *kf, *af, *vf, *sc, *dec;
 };
 
@@ -224,10 +229,28 @@ __global__ void __launch_bounds__(REC_THREADS) recurrence_prep_kernel(RecArgs a)
     }
     if (MODE == MODE_DELTA) {
       const float neg_a = -expf(load_w(a.a_log, a.par_dtype, h));
-      const T* rr = (const T*)a.rate + (size_t)t * a.rate_stride + (size_t)h * dk;
       float* ao = a.af + ((size_t)t * a.H + h) * dkp;
-      for (int i = tid; i < dkp; i += REC_THREADS)
-        ao[i] = i < dk ? expf(neg_a * softplus_f(to_float(rr[i]) + load_w(a.dt_bias, a.par_dtype, (size_t)h * dk + i))) : 1.f;
+      if (a.rate_per_head) {                   // one decay for all rows of the head's state
+        const float g = expf(neg_a * softplus_f(load_w(a.rate, a.rate_dtype, (size_t)t * a.rate_stride + h) + load_w(a.dt_bias, a.par_dtype, h)));
+        for (int i = tid; i < dkp; i += REC_THREADS) ao[i] = i < dk ? g : 1.f;
+      } else {
+        const size_t r0 = (size_t)t * a.rate_stride + (size_t)h * dk;
+        for (int i = tid; i < dkp; i += REC_THREADS)
+          ao[i] = i < dk ? expf(neg_a * softplus_f(load_w(a.rate, a.rate_dtype, r0 + i) + load_w(a.dt_bias, a.par_dtype, (size_t)h * dk + i))) : 1.f;
+      }
+    }
+    float bonus_dot = 0.f;
+    if (MODE == MODE_WKV) {
+      // (H == Hqk here: every head has a receptance and a key of its own)
+      const size_t r0 = (size_t)t * a.rate_stride + (size_t)h * dk;
+      const T* qr = (const T*)a.q + (size_t)t * a.q_stride + (size_t)h * dk;
+      const T* kr = (const T*)a.k + (size_t)t * a.k_stride + (size_t)h * dk;
+      float* ao = a.af + ((size_t)t * a.H + h) * dkp;
+      for (int i = tid; i < dkp; i += REC_THREADS) {
+        ao[i] = i < dk ? expf(-expf(load_w(a.rate, a.rate_dtype, r0 + i) + load_w(a.dt_bias, a.par_dtype, (size_t)h * dk + i))) : 1.f;
+        if (i < dk) bonus_dot += to_float(qr[i]) * a.bonus[(size_t)h * dk + i] * to_float(kr[i]);
+      }
+      bonus_dot = block_sum(bonus_dot, red);
     }
     if (tid == 0) {
       float sc = 1.f, dec = 1.f;
@@ -237,6 +260,7 @@ __global__ void __launch_bounds__(REC_THREADS) recurrence_prep_kernel(RecArgs a)
         dec = expf(-expf(load_w(a.a_log, a.par_dtype, h)) * sc);
       }
       if (MODE == MODE_DELTA) sc = sigmoid_f(to_float(((const T*)a.aux)[(size_t)t * a.aux_stride + h]));
+      if (MODE == MODE_WKV) sc = bonus_dot;
       a.sc[(size_t)t * a.H + h] = sc;
       a.dec[(size_t)t * a.H + h] = dec;
     }
@@ -251,12 +275,14 @@ __device__ __forceinline__ void rec_cp4(float* smem, const float* g) {
 }
 
 // grid (dvp / VC, H, rows); 128 threads; VC = 128 / P columns a block.
-template <bool DELTA, bool SKIP>
+template <int MODE>
 __global__ void __launch_bounds__(REC_THREADS) recurrence_scan_kernel(RecArgs a) {
+  constexpr bool DELTA = MODE == MODE_DELTA, SKIP = MODE == MODE_SSM, WKV = MODE == MODE_WKV;
+  constexpr bool ROWS = DELTA || WKV;                                 // a decay per row of S comes with every token
   extern __shared__ __align__(16) float smem[];
   const int dk = a.dk, dv = a.dv, P = a.P, dkp = a.dkp, dvp = a.dvp, H = a.H;
   const int VC = REC_THREADS / P;
-  const int per_tok = (DELTA ? 3 : 2) * dkp + VC;                    // floats of a token's vectors in a stage
+  const int per_tok = (ROWS ? 3 : 2) * dkp + VC;                     // floats of a token's vectors in a stage
   const int stage_floats = REC_TS * per_tok + 2 * REC_TS;             // + sc, dec
   const int r = blockIdx.z, h = blockIdx.y, j0 = blockIdx.x * VC;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -285,12 +311,12 @@ __global__ void __launch_bounds__(REC_THREADS) recurrence_scan_kernel(RecArgs a)
       float* dst = base + (size_t)tt * per_tok;
       rec_cp16(dst + c, a.qf + (tok * a.Hqk + hq) * dkp + c);
       rec_cp16(dst + dkp + c, a.kf + (tok * a.Hqk + hq) * dkp + c);
-      if (DELTA) rec_cp16(dst + 2 * dkp + c, a.af + (tok * H + h) * dkp + c);
+      if (ROWS) rec_cp16(dst + 2 * dkp + c, a.af + (tok * H + h) * dkp + c);
     }
     const int v16 = VC / 4;
     for (int w = tid; w < nt * v16; w += REC_THREADS) {
       const int tt = w / v16, c = (w - tt * v16) * 4;
-      rec_cp16(base + (size_t)tt * per_tok + (DELTA ? 3 : 2) * dkp + c, a.vf + ((size_t)(q0 + t0 + tt) * H + h) * dvp + j0 + c);
+      rec_cp16(base + (size_t)tt * per_tok + (ROWS ? 3 : 2) * dkp + c, a.vf + ((size_t)(q0 + t0 + tt) * H + h) * dvp + j0 + c);
     }
     for (int w = tid; w < 2 * nt; w += REC_THREADS) {
       const int tt = w >> 1;
@@ -313,13 +339,29 @@ __global__ void __launch_bounds__(REC_THREADS) recurrence_scan_kernel(RecArgs a)
       const float4* q4 = reinterpret_cast<const float4*>(base + (size_t)tt * per_tok);
       const float4* k4 = q4 + dkp / 4;
       const float4* a4 = k4 + dkp / 4;
-      const float vv = base[(size_t)tt * per_tok + (DELTA ? 3 : 2) * dkp + col];
+      const float vv = base[(size_t)tt * per_tok + (ROWS ? 3 : 2) * dkp + col];
       const float sc = base[REC_TS * per_tok + 2 * tt], dec = base[REC_TS * per_tok + 2 * tt + 1];
       float4 kk[4], qq[4];
 #pragma unroll
       for (int x4 = 0; x4 < 4; ++x4) {
         kk[x4] = k4[x4 * P + part];
         qq[x4] = q4[x4 * P + part];
+      }
+      if (WKV) {
+        // the read-out sees the state the tokens before left, and this token's own k v^T through the bonus (sc)
+        float oo[4];
+#pragma unroll
+        for (int x4 = 0; x4 < 4; ++x4) {
+          const float4 aa = a4[x4 * P + part];
+          oo[x4] = s[4 * x4] * qq[x4].x + s[4 * x4 + 1] * qq[x4].y + s[4 * x4 + 2] * qq[x4].z + s[4 * x4 + 3] * qq[x4].w;
+          s[4 * x4] = s[4 * x4] * aa.x + kk[x4].x * vv; s[4 * x4 + 1] = s[4 * x4 + 1] * aa.y + kk[x4].y * vv;
+          s[4 * x4 + 2] = s[4 * x4 + 2] * aa.z + kk[x4].z * vv; s[4 * x4 + 3] = s[4 * x4 + 3] * aa.w + kk[x4].w * vv;
+        }
+        float o_acc = (oo[0] + oo[1]) + (oo[2] + oo[3]);
+        for (int o = P >> 1; o > 0; o >>= 1) o_acc += __shfl_xor_sync(0xffffffffu, o_acc, o);
+        o_acc += sc * vv;
+        if (part == 0 && col_ok) a.out[(size_t)(q0 + t0 + tt) * a.out_stride + (size_t)h * dv + j] = o_acc;
+        continue;
       }
       float u;
       if (DELTA) {
@@ -367,7 +409,7 @@ static inline int rec_lanes(int dk) {
 
 static inline long long rec_work_floats(int mode, int n_tokens, int H, int Hqk, int dk, int dv) {
   const int P = rec_lanes(dk), dkp = P * REC_RPT, VC = REC_THREADS / P, dvp = (dv + VC - 1) / VC * VC;
-  return (long long)n_tokens * ((long long)2 * Hqk * dkp + (mode == MODE_DELTA ? (long long)H * dkp : 0) + (long long)H * dvp + 2 * H) + 16;
+  return (long long)n_tokens * ((long long)2 * Hqk * dkp + ((mode == MODE_DELTA || mode == MODE_WKV) ? (long long)H * dkp : 0) + (long long)H * dvp + 2 * H) + 16;
 }
 
 template <typename T, int MODE>
@@ -382,16 +424,16 @@ int launch_recurrence(RecArgs a, float* work, int n_rows, cudaStream_t stream) {
   a.qf = work;
   a.kf = a.qf + T_ * a.Hqk * a.dkp;
   a.af = a.kf + T_ * a.Hqk * a.dkp;
-  a.vf = a.af + (MODE == MODE_DELTA ? T_ * a.H * a.dkp : 0);
+  a.vf = a.af + ((MODE == MODE_DELTA || MODE == MODE_WKV) ? T_ * a.H * a.dkp : 0);
   a.sc = a.vf + T_ * a.H * a.dvp;
   a.dec = a.sc + T_ * a.H;
   if (a.n_tokens > 0x7fffffff / 1 || a.H > 65535 || a.Hqk > 65535) return SB_ERR_LIMIT;
   recurrence_prep_kernel<T, MODE><<<dim3(a.n_tokens, a.H > a.Hqk ? a.H : a.Hqk), REC_THREADS, 0, stream>>>(a);
   SB_LAUNCH_CHECK();
-  const int per_tok = (MODE == MODE_DELTA ? 3 : 2) * a.dkp + VC;
+  const int per_tok = ((MODE == MODE_DELTA || MODE == MODE_WKV) ? 3 : 2) * a.dkp + VC;
   const size_t smem = (size_t)2 * (REC_TS * per_tok + 2 * REC_TS) * sizeof(float);
   dim3 grid(a.dvp / VC, a.H, n_rows);
-  auto kernel = recurrence_scan_kernel<MODE == MODE_DELTA, MODE == MODE_SSM>;
+  auto kernel = recurrence_scan_kernel<MODE>;
   if (smem > 48 * 1024) {
     if (smem > 200 * 1024) return SB_ERR_LIMIT;
     cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -486,7 +528,67 @@ __global__ void __launch_bounds__(128) kv_norm_cache_write_kernel(const T* __res
   }
 }
 
+// ------------------------------------------------------------------------------------------ token shift
+// out[m, t, c] = x[t, c] + (x[t - 1, c] - x[t, c]) * mu[m, c] for each of n_mix blends; before a row's first token stands
+// the row's state (float [slots, C]: the input of the request's last token so far, zeros at the start). A thread per
+// (token, channel) computes every blend of it. With one token a row (pure_decode) the same thread then stores its
+// input as the new state; otherwise token_shift_state_kernel does, in a launch of its own after every read.
+template <typename T>
+__global__ void __launch_bounds__(256) token_shift_kernel(const T* __restrict__ x, int x_stride, const float* __restrict__ mu, int n_mix,
+                                                          float* __restrict__ state, long long slot_stride, const int* __restrict__ slots,
+                                                          const int* __restrict__ cu_q, const int* __restrict__ token_row,
+                                                          T* __restrict__ out, long long mix_stride, int out_stride, int C, int pure_decode) {
+  const int t = blockIdx.y;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const int r = token_row[t];
+  const float cur = to_float(x[(size_t)t * x_stride + c]);
+  float* st = state + (size_t)slots[r] * slot_stride + c;
+  const float prev = t > cu_q[r] ? to_float(x[(size_t)(t - 1) * x_stride + c]) : *st;
+  const float d = prev - cur;
+  for (int m = 0; m < n_mix; ++m) out[(size_t)m * mix_stride + (size_t)t * out_stride + c] = from_float<T>(cur + d * mu[(size_t)m * C + c]);
+  if (pure_decode) *st = cur;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) token_shift_state_kernel(const T* __restrict__ x, int x_stride, float* __restrict__ state,
+                                                                long long slot_stride, const int* __restrict__ slots,
+                                                                const int* __restrict__ cu_q, int C) {
+  const int r = blockIdx.y;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int last = cu_q[r + 1] - 1;
+  if (c >= C || last < cu_q[r]) return;
+  state[(size_t)slots[r] * slot_stride + c] = to_float(x[(size_t)last * x_stride + c]);
+}
+
 }  // namespace
+
+// x [T, C] (row stride x_stride), mu float [n_mix, C], state float [slots, C] (slots slot_stride floats apart), out
+// [n_mix, T, C] (blends mix_stride apart, rows out_stride apart).
+SB_EXPORT int sb_token_shift(const void* x, int x_stride, const float* mu, int n_mix, float* state, long long slot_stride, const int* slots,
+                             const int* cu_q, const int* token_row, void* out, long long mix_stride, int out_stride, int C, int n_tokens,
+                             int n_rows, int pure_decode, int dtype, cudaStream_t stream) {
+  if (n_tokens <= 0 || C <= 0) return 0;
+  if (n_mix <= 0 || !state || x == out) return SB_ERR_SHAPE;
+  if (n_tokens > 65535 || n_rows > 65535 || n_rows <= 0) return SB_ERR_LIMIT;
+  dim3 grid((C + 255) / 256, n_tokens), sgrid(grid.x, n_rows);
+  if (dtype == SB_DTYPE_F32) {
+    token_shift_kernel<float><<<grid, 256, 0, stream>>>((const float*)x, x_stride, mu, n_mix, state, slot_stride, slots, cu_q, token_row,
+                                                         (float*)out, mix_stride, out_stride, C, pure_decode);
+    SB_LAUNCH_CHECK();
+    if (!pure_decode) token_shift_state_kernel<float><<<sgrid, 256, 0, stream>>>((const float*)x, x_stride, state, slot_stride, slots, cu_q, C);
+  } else if (dtype == SB_DTYPE_BF16) {
+    typedef __nv_bfloat16 B;
+    token_shift_kernel<B><<<grid, 256, 0, stream>>>((const B*)x, x_stride, mu, n_mix, state, slot_stride, slots, cu_q, token_row, (B*)out,
+                                                     mix_stride, out_stride, C, pure_decode);
+    SB_LAUNCH_CHECK();
+    if (!pure_decode) token_shift_state_kernel<B><<<sgrid, 256, 0, stream>>>((const B*)x, x_stride, state, slot_stride, slots, cu_q, C);
+  } else {
+    return SB_ERR_DTYPE;
+  }
+  SB_LAUNCH_CHECK();
+  return 0;
+}
 
 // x [T, C] (row stride x_stride), w [C, taps], bias [C] or null, state float [slots, taps - 1, C], out [T, C].
 // act: 0 none, 1 silu. residual: the input itself is added before the activation. A step in which every row brings one
@@ -535,21 +637,26 @@ SB_EXPORT long long sb_linear_recurrence_work_floats(int mode, int n_tokens, int
   return rec_work_floats(mode, n_tokens, H, Hqk, dk, dv);
 }
 
-// The three recurrences (mode 0: fixed decay per head with silu on q, k, v; 1: selective state space; 2: gated delta
-// rule). See RecArgs for what each pointer is; unused ones are null. out is float [T, H * dv]; work: 16-byte aligned floats,
+// The recurrences (mode 0: fixed decay per head with silu on q, k, v; 1: selective state space; 2: gated delta rule, its
+// rate per row of the state or, with rate_per_head, per head; 3: decay per key channel with a bonus [H, dk] for the
+// current token, read out before the update). See RecArgs for what each pointer is; unused ones are null. ``rate`` has a
+// dtype of its own (rate_dtype). out is float [T, H * dv]; work: 16-byte aligned floats,
 // as many as sb_linear_recurrence_work_floats says.
 SB_EXPORT int sb_linear_recurrence(int mode, const void* q, int q_stride, const void* k, int k_stride, const void* v, int v_stride,
-                                   const void* aux, int aux_stride, const void* rate, int rate_stride, const float* decay,
-                                   const void* a_log, const void* dt_bias, const void* d_skip, int par_dtype, float* state,
+                                   const void* aux, int aux_stride, const void* rate, int rate_stride, int rate_dtype, int rate_per_head,
+                                   const float* bonus, const float* decay, const void* a_log, const void* dt_bias, const void* d_skip, int par_dtype, float* state,
                                    const int* slots, const int* cu_q, float* out, int out_stride, int H, int Hqk, int dk, int dv,
                                    float q_scale, int n_rows, int n_tokens, float* work, long long state_stride, int dtype, cudaStream_t stream) {
   if (n_rows <= 0 || n_tokens <= 0) return 0;
   if (!work || !aligned16(work)) return SB_ERR_ALIGN;
   if (H <= 0 || Hqk <= 0 || H % Hqk || dk <= 0 || dv <= 0) return SB_ERR_SHAPE;
   if (n_rows > 65535 || H > 65535 || dk > 32 * REC_RPT) return SB_ERR_LIMIT;
+  if (mode == MODE_WKV && (H != Hqk || !rate || !dt_bias || !bonus)) return SB_ERR_SHAPE;
+  if (rate && rate_dtype != SB_DTYPE_F32 && rate_dtype != SB_DTYPE_BF16) return SB_ERR_DTYPE;
   RecArgs a;
   a.q = q; a.k = k; a.v = v; a.q_stride = q_stride; a.k_stride = k_stride; a.v_stride = v_stride;
-  a.aux = aux; a.aux_stride = aux_stride; a.rate = rate; a.rate_stride = rate_stride; a.decay = decay;
+  a.aux = aux; a.aux_stride = aux_stride; a.rate = rate; a.rate_stride = rate_stride; a.rate_dtype = rate_dtype;
+  a.rate_per_head = rate_per_head; a.bonus = bonus; a.decay = decay;
   a.a_log = a_log; a.dt_bias = dt_bias; a.d_skip = d_skip; a.par_dtype = par_dtype; a.state = state; a.state_stride = state_stride; a.slots = slots; a.cu_q = cu_q;
   a.out = out; a.out_stride = out_stride; a.H = H; a.Hqk = Hqk; a.dk = dk; a.dv = dv; a.P = 1; a.dkp = a.dvp = 0; a.n_tokens = n_tokens;
   a.q_scale = q_scale; a.qf = a.kf = a.af = a.vf = a.sc = a.dec = nullptr;
@@ -557,10 +664,12 @@ SB_EXPORT int sb_linear_recurrence(int mode, const void* q, int q_stride, const 
     if (mode == MODE_DECAY) return launch_recurrence<float, MODE_DECAY>(a, work, n_rows, stream);
     if (mode == MODE_SSM) return launch_recurrence<float, MODE_SSM>(a, work, n_rows, stream);
     if (mode == MODE_DELTA) return launch_recurrence<float, MODE_DELTA>(a, work, n_rows, stream);
+    if (mode == MODE_WKV) return launch_recurrence<float, MODE_WKV>(a, work, n_rows, stream);
   } else if (dtype == SB_DTYPE_BF16) {
     if (mode == MODE_DECAY) return launch_recurrence<__nv_bfloat16, MODE_DECAY>(a, work, n_rows, stream);
     if (mode == MODE_SSM) return launch_recurrence<__nv_bfloat16, MODE_SSM>(a, work, n_rows, stream);
     if (mode == MODE_DELTA) return launch_recurrence<__nv_bfloat16, MODE_DELTA>(a, work, n_rows, stream);
+    if (mode == MODE_WKV) return launch_recurrence<__nv_bfloat16, MODE_WKV>(a, work, n_rows, stream);
   } else {
     return SB_ERR_DTYPE;
   }

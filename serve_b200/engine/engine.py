@@ -102,7 +102,9 @@ class Engine:
             # the share is what the memory fraction pays for, at most all of it.
             keys = CacheManager.group_keys(needs)
             per_page = CacheManager.bytes_per_page(needs, ec.page_size, self.dtype.itemsize)
-            most = [ec.max_slots * CacheManager.most_pages_of_a_request(key[2], ec.page_size, self.max_context, ec.max_tokens_per_step, key[3])
+            kept = lambda key: -(-key[key.index("keep_first") + 1] // ec.page_size) if "keep_first" in key else 0
+            most = [ec.max_slots * CacheManager.most_pages_of_a_request(key[2], ec.page_size, self.max_context, ec.max_tokens_per_step, key[3],
+                                                                        kept(key))
                     for key in keys]
             share = 1.0
             if self.rt.device.type == "cuda" and keys:

@@ -294,6 +294,53 @@ class CudaKernels:
         _check(self._prep_lib().sb_add_layernorm(_p(x), _p(delta), _p(rows), _p(weight), _DT[weight.dtype], _p(out), rows.shape[0],
                                                  x.shape[1], ctypes.c_float(eps), _DT[out.dtype], self._s()), "add_layernorm_rows")
 
+    def add_dynamic_tanh(self, x, delta, through, rows, params, out) -> None:
+        """x += d; out = tanh(alpha x) w + b with params = float [w | b | alpha]. d is ``delta`` (activations or float), or, with
+        ``through`` (the parameters of the dynamic tanh the delta still has to pass), tanh(alpha' delta) w' + b'. With ``rows``
+        only those rows, and x stays as it is; with x None, out = the dynamic tanh of delta."""
+        self.launches += 1
+        n_rows = rows.shape[0] if rows is not None else out.shape[0]
+        _check(self._prep_lib().sb_add_dynamic_tanh(_p(x), _p(delta), _DT[delta.dtype] if delta is not None else 0, _p(through), _p(rows),
+                                                    _p(params), _p(out), _DT[out.dtype], n_rows, out.shape[1], self._s()), "dynamic tanh")
+
+    _ACTIVATIONS = {"relu_squared": 0, "gelu_tanh": 1, "silu": 2, "tanh": 3}
+
+    def activation(self, x, out, kind: str, bias=None) -> None:
+        """out = act(x + bias) element by element, in float, rounded once (x and out contiguous; may be the same buffer)."""
+        if not x.is_contiguous() or not out.is_contiguous() or x.shape != out.shape or x.dtype != out.dtype:
+            raise KernelError("activation: x and out must be contiguous and alike")
+        self.launches += 1
+        _check(self._prep_lib().sb_activation(_p(x), _p(bias), _p(out), x.shape[0], x.shape[1], self._ACTIVATIONS[kind], _DT[x.dtype],
+                                              self._s()), "activation")
+
+    def linear_activation(self, h, w, out, kind: str) -> None:
+        """out = act(h @ w^T): the product, then the activation in place."""
+        self.linear(h, w, out)
+        self.activation(out, out, kind)
+
+    def add_bias(self, x, bias) -> None:
+        """x (float, contiguous) += bias (float) along the rows."""
+        if x.dtype != torch.float32 or bias.dtype != torch.float32 or not x.is_contiguous():
+            raise KernelError("add_bias: float, contiguous operands")
+        self.launches += 1
+        _check(self._prep_lib().sb_add_bias(_p(x), _p(bias), x.shape[0], x.shape[1], self._s()), "bias")
+
+    def qk_prepare(self, sums, bias, positions, token_row, heads, kv_heads, head_dim, dim, q_weight, k_weight, eps, inv_freq, rot_dims,
+                   q_out, k_cache, v_cache, block_table, page_size) -> None:
+        """From the float sums of a fused query | key | value projection [T, (H + 2 G) * D] (heads padded to D; G = 0: queries only):
+        bias added, all queries (all keys) of a token divided by their root mean square over H * dim (G * dim) true elements and
+        multiplied by float weights laid out like the padded projection (None: no norm), the first rot_dims elements of every
+        query and key head rotated (pairs i, i + rot_dims / 2), queries to q_out, keys and values to their pages."""
+        if sums.dtype != torch.float32:
+            raise KernelError("qk_prepare: the projection's sums are float")
+        self.launches += 1
+        pages = k_cache.shape[0] if k_cache is not None else 0
+        _check(self._prep_lib().sb_qk_prepare(
+            _p(sums), sums.stride(0), _p(bias), _p(positions), _p(token_row), heads, kv_heads, head_dim, dim, _p(q_weight), _p(k_weight),
+            ctypes.c_float(eps), _p(inv_freq), int(rot_dims), _p(q_out), q_out.stride(0), _p(k_cache if kv_heads else None),
+            _p(v_cache if kv_heads else None), _p(block_table), block_table.shape[1], page_size, pages, _p(self.errors_tensor()),
+            sums.shape[0], _DT[q_out.dtype], self._s()), "query/key preparation")
+
     def linear_batched(self, a, w, out) -> None:
         """out[:, b] = a[:, b] @ w[b]^T for every b: a [M, B, K] and out [M, B, N] may be views of wider buffers (unit stride
         along the last axis), w [B, N, K] is whole. One batched library product."""
@@ -485,24 +532,29 @@ class CudaKernels:
                               k_cache, v_cache, block_table, page_size, write_cache)
 
     def attention(self, qkv, k_cache, v_cache, block_table, cu_q, kv_len, token_row, positions, heads, kv_heads, head_dim,
-                  page_size, scale, window, out, shape, slopes=None, chunk: int = 0, softcap: float = 0.0, sinks=None) -> None:
+                  page_size, scale, window, out, shape, slopes=None, chunk: int = 0, softcap: float = 0.0, sinks=None,
+                  keep_first: int = 0) -> None:
         """``slopes`` (float [heads]): slope_h * distance is taken off every score; ``chunk`` > 0: a query sees only the keys of
         its own block of ``chunk`` positions; ``softcap`` c > 0: a scaled score s becomes c * tanh(s / c); ``sinks`` (float
-        [heads]): exp(sink_h) joins the softmax's denominator. In bfloat16 all run on the mma.sync kernels; cap and sink
+        [heads]): exp(sink_h) joins the softmax's denominator; ``keep_first`` n > 0 (with a window): the sequence's first n keys
+        stay visible to every later query. In bfloat16 all run on the mma.sync kernels; cap and sink
         also on the tensor-memory kernel (prompt portions at head sizes 64 and 128); in float32 on the plain-arithmetic kernel."""
         lib = self._attention_lib(head_dim)
         softcap = float(softcap or 0.0)
-        opts = slopes is not None or chunk or softcap > 0.0 or sinks is not None
+        keep_first = int(keep_first or 0) if window else 0
+        opts = slopes is not None or chunk or softcap > 0.0 or sinks is not None or keep_first > 0
         if opts and qkv.dtype == torch.bfloat16 and not self.force_simt_attention:
             return self._attention_mma(lib, qkv, k_cache, v_cache, block_table, cu_q, kv_len, heads, kv_heads, head_dim,
-                                       page_size, scale, window, out, shape, slopes=slopes, chunk=int(chunk), softcap=softcap, sinks=sinks)
+                                       page_size, scale, window, out, shape, slopes=slopes, chunk=int(chunk), softcap=softcap, sinks=sinks,
+                                       keep_first=keep_first)
         if opts:
             group = heads // kv_heads
             self.launches += (1 if group <= 16 else 0) + (1 if group > 16 or shape.max_q * group > 16 else 0)
-            _check(lib.sb_attention_simt_opts(
+            _check(lib.sb_attention_simt_keep(
                 _p(qkv), qkv.stride(0), _p(k_cache), _p(v_cache), _p(block_table), block_table.shape[1], _p(cu_q), _p(kv_len),
                 heads, kv_heads, page_size, k_cache.shape[0], ctypes.c_float(scale), window, _p(out), shape.rows, shape.max_q,
-                _DT[qkv.dtype], _p(slopes), int(chunk), ctypes.c_float(softcap), _p(sinks), self._s()), "attention with score options")
+                _DT[qkv.dtype], _p(slopes), int(chunk), ctypes.c_float(softcap), _p(sinks), keep_first, self._s()),
+                "attention with score options")
             return
         if qkv.dtype == torch.bfloat16 and not self.force_simt_attention:
             return self._attention_mma(lib, qkv, k_cache, v_cache, block_table, cu_q, kv_len, heads, kv_heads, head_dim,
@@ -530,7 +582,8 @@ class CudaKernels:
         return max(1, min(want, -(-max_kv // 256), self.MAX_SPLITS))
 
     def _attention_mma(self, lib, qkv, k_cache, v_cache, block_table, cu_q, kv_len, heads, kv_heads, head_dim, page_size,
-                       scale, window, out, shape, slopes=None, chunk: int = 0, softcap: float = 0.0, sinks=None) -> None:
+                       scale, window, out, shape, slopes=None, chunk: int = 0, softcap: float = 0.0, sinks=None,
+                       keep_first: int = 0) -> None:
         # One cached row for many query heads (keys and values the same tensor): the heads are dealt to groups of LATENT_GROUP
         # that each count as a kv head reading the same rows. A decoding request is then several (request, kv head) pairs of
         # few rows, which the deep shape spreads over the SMs with its key splits; as one pair of 32 rows it would be a single
@@ -565,12 +618,13 @@ class CudaKernels:
             wide_rows = shape.rows_by_q
         num_splits, scratch, tickets = 1, None, None
         if which & 2:
-            num_splits = self.split_plan(shape.rows, kv_heads, shape.max_kv)
+            # (behind a window a query reads at most the window's keys and the kept first ones, however long the sequence)
+            num_splits = self.split_plan(shape.rows, kv_heads, min(shape.max_kv, window + keep_first + 16) if window else shape.max_kv)
             if num_splits > 1:
                 scratch = self._scratch_buffer(lib, shape.rows, kv_heads, num_splits)
                 tickets = self._ticket_buffer(shape.rows * kv_heads)
         by_distance = slopes is not None or chunk > 0 or softcap > 0.0 or sinks is not None
-        if (which & 1) and slopes is None and not chunk and kv_div == 1 and self.use_tcgen05_attention and self._tc_attention_takes(lib, heads, kv_heads, head_dim, page_size, window, qkv.shape[1]):
+        if (which & 1) and slopes is None and not chunk and not keep_first and kv_div == 1 and self.use_tcgen05_attention and self._tc_attention_takes(lib, heads, kv_heads, head_dim, page_size, window, qkv.shape[1]):
             # prompt portions on the tensor-memory path; what is left (decoding rows) goes to the deep shape below
             self.launches += 1
             _check(lib.sb_attention_tc_opts(
@@ -582,11 +636,11 @@ class CudaKernels:
             if not which:
                 return
         self.launches += (which & 1) + ((which >> 1) & 1) + ((which >> 2) & 1)
-        _check(lib.sb_attention_mma_opts(
+        _check(lib.sb_attention_mma_keep(
             _p(qkv), qkv.stride(0), _p(k_cache), _p(v_cache), _p(block_table), block_table.shape[1], _p(cu_q), _p(kv_len),
             heads, kv_heads, page_size, k_cache.shape[0], ctypes.c_float(scale), window, _p(out), shape.rows, shape.max_q,
             which, int(shape.max_kv), num_splits, _p(scratch), _p(tickets), _p(wide_rows), n_wide, _p(slopes), chunk,
-            ctypes.c_float(softcap), _p(sinks), kv_div, self._s()), "attention")
+            ctypes.c_float(softcap), _p(sinks), kv_div, keep_first, self._s()), "attention")
 
     def _tc_attention_takes(self, lib, heads, kv_heads, head_dim, page_size, window, stride) -> bool:
         key = (heads, kv_heads, head_dim, page_size, window, stride)
@@ -777,15 +831,31 @@ class CudaKernels:
             1 if ctx.shape.pure_decode else 0, ctypes.c_longlong(state.stride(0) if state is not None else 0), _DT[x.dtype], self._s()),
             "short convolution")
 
+    def token_shift_mix(self, x, mu, state, ctx, out) -> None:
+        """out[m, t] = x[t] + (x[t - 1] - x[t]) * mu[m] over each request's own tokens; before a portion's first token stands
+        ``state`` [slots, 1, C] (float), which then takes the portion's last input. out [n_mix, T, C]."""
+        c = x.shape[1]
+        if mu.dtype != torch.float32 or mu.shape[1] != c or tuple(out.shape) != (mu.shape[0], x.shape[0], c) or out.stride(2) != 1 or x.stride(1) != 1:
+            raise KernelError("token_shift_mix: shapes do not fit")
+        self.launches += 1 if ctx.shape.pure_decode else 2
+        _check(self._seq_lib().sb_token_shift(
+            _p(x), x.stride(0), _p(mu), mu.shape[0], _p(state), ctypes.c_longlong(state.stride(0)), _p(ctx.slots), _p(ctx.cu_q),
+            _p(ctx.token_row), _p(out), ctypes.c_longlong(out.stride(0)), out.stride(1), c, x.shape[0], ctx.shape.rows,
+            1 if ctx.shape.pure_decode else 0, _DT[x.dtype], self._s()), "token shift")
+
     def linear_recurrence(self, mode: str, q, k, v, state, ctx, out, heads: int, qk_heads: int, dk: int, dv: int, aux=None, rate=None,
-                          decay=None, a_log=None, dt_bias=None, d_skip=None, q_scale: float = 1.0) -> None:
+                          decay=None, a_log=None, dt_bias=None, d_skip=None, q_scale: float = 1.0, rate_per_head: bool = False,
+                          bonus=None) -> None:
         """One matrix state [dk, dv] per (request, head), walked over the step's tokens: see csrc/sequence_ops.cu.
         mode "decay": S = decay_h S + k v^T with silu on q, k, v; "ssm": S = exp(-exp(a_log) dt) S + dt k v^T, dt =
         softplus(aux + dt_bias), o += d_skip v; "delta": S = g S, S += k (beta (v - S^T k))^T with g = exp(-exp(a_log)
-        softplus(rate + dt_bias)), beta = sigmoid(aux), q and k made unit vectors. out: float [T, heads * dv]."""
+        softplus(rate + dt_bias)), beta = sigmoid(aux), q and k made unit vectors (``rate_per_head``: rate [T, heads] and dt_bias
+        [heads], one decay for a head's whole state); "wkv": o = S^T q + (sum_i q_i bonus_i k_i) v, then S = diag(d) S + k v^T
+        with d = exp(-exp(rate + dt_bias)) per row (rate [T, heads * dk], of a dtype of its own; bonus float [heads * dk]).
+        out: float [T, heads * dv]."""
         par = a_log if a_log is not None else None
         lib = self._seq_lib()
-        code = {"decay": 0, "ssm": 1, "delta": 2}[mode]
+        code = {"decay": 0, "ssm": 1, "delta": 2, "wkv": 3}[mode]
         lib.sb_linear_recurrence_work_floats.restype = ctypes.c_longlong
         need = lib.sb_linear_recurrence_work_floats(code, q.shape[0], heads, qk_heads, dk, dv)
         if need < 0:
@@ -794,7 +864,8 @@ class CudaKernels:
         self.launches += 2
         _check(lib.sb_linear_recurrence(
             code, _p(q), q.stride(0), _p(k), k.stride(0), _p(v), v.stride(0),
-            _p(aux), aux.stride(0) if aux is not None else 0, _p(rate), rate.stride(0) if rate is not None else 0, _p(decay),
+            _p(aux), aux.stride(0) if aux is not None else 0, _p(rate), rate.stride(0) if rate is not None else 0,
+            _DT[rate.dtype] if rate is not None else 0, 1 if rate_per_head else 0, _p(bonus), _p(decay),
             _p(a_log), _p(dt_bias), _p(d_skip), _DT[par.dtype] if par is not None else 0, _p(state), _p(ctx.slots), _p(ctx.cu_q),
             _p(out), out.stride(0), heads, qk_heads, dk, dv, ctypes.c_float(q_scale), ctx.shape.rows, q.shape[0], _p(work),
             ctypes.c_longlong(state.stride(0)), _DT[v.dtype], self._s()),
@@ -822,11 +893,22 @@ class CudaKernels:
             _DT[qkv.dtype], self._s()), "cache write with value norm")
 
     def routed_experts(self, h, logits, w_gate_up, w_down, top: int, out, score: str = "sigmoid", renormalise: bool = False,
-                       scale_input: bool = True, activation: str = "clamped_swish", limit: float = 0.0, alpha: float = 1.702) -> None:
+                       scale_input: bool = True, activation: str = "clamped_swish", limit: float = 0.0, alpha: float = 1.702,
+                       outputs=None, choice_bias=None, renormalise_eps: float = 0.0, shared=None, shared_gated: bool = False) -> None:
         """out[t] = sum over the ``top`` best experts e of expert_e(w_e * h[t]) (or w_e * expert_e(h[t])): logits float [T, E],
-        w_gate_up [E, 2 ff, K], w_down [E, N, ff]."""
+        w_gate_up [E, 2 ff, K], w_down [E, N, ff]. More: the router scores the first ``outputs`` columns of logits, of which those
+        beyond the E experts stand for the token's input itself; ``choice_bias`` (float [outputs]) joins the scores for the choice
+        only; ``renormalise_eps`` joins the sum the weights are divided by; ``shared`` [T, N] is added for every token, times
+        sigmoid(logits[:, outputs]) if ``shared_gated``."""
         lib = self._moe_lib()
-        t, e = logits.shape
+        t = logits.shape[0]
+        e = w_down.shape[0]
+        more = outputs is not None
+        if not more and logits.shape[1] != e:
+            raise KernelError("routed_experts: one router logit per expert")
+        if more and (scale_input or outputs < e or logits.shape[1] < outputs + (1 if shared_gated else 0)
+                     or (outputs > e and w_down.shape[1] != h.shape[1])):
+            raise KernelError("routed_experts: identity experts, a choice bias and a shared expert come with weights on the outputs")
         ff, n, k = w_down.shape[2], w_down.shape[1], h.shape[1]
         pairs = t * top
         dev = h.device
@@ -840,17 +922,27 @@ class CudaKernels:
         wts = torch.empty(pairs, dtype=torch.float32, device=dev)
         s = self._s()
         self.launches += 4
-        _check(lib.sb_moe_route(_p(logits), e, top, {"sigmoid": 0, "softmax": 1}[score], 1 if renormalise else 0, t, _p(idx), _p(wts), s),
-               "expert choice")
+        if more:
+            _check(lib.sb_moe_route_bias(_p(logits), logits.stride(0), outputs, top, {"sigmoid": 0, "softmax": 1}[score],
+                                         1 if renormalise else 0, ctypes.c_float(renormalise_eps), _p(choice_bias), t, _p(idx), _p(wts), s),
+                   "expert choice")
+        else:
+            _check(lib.sb_moe_route(_p(logits), e, top, {"sigmoid": 0, "softmax": 1}[score], 1 if renormalise else 0, t, _p(idx), _p(wts), s),
+                   "expert choice")
         _check(lib.sb_moe_sort(_p(idx), pairs, e, tile_rows, _p(offsets), _p(order), _p(tiles), _p(n_tiles), s), "grouping by expert")
         act = torch.empty((pairs, ff), dtype=h.dtype, device=dev)
         _check(lib.sb_moe_gate_up(_p(h), h.stride(0), _p(w_gate_up), _p(order), _p(offsets), _p(tiles), _p(n_tiles), _p(wts), top, pairs,
                                   e, k, ff, 1 if scale_input else 0, {"swiglu": 0, "clamped_swish": 1}[activation],
                                   ctypes.c_float(limit), ctypes.c_float(alpha), _p(act), _DT[h.dtype], s), "experts, gate and up")
-        parts = out if top == 1 else torch.empty((pairs, n), dtype=torch.float32, device=dev)
+        parts = out if (top == 1 and not more) else torch.empty((pairs, n), dtype=torch.float32, device=dev)
         _check(lib.sb_moe_down(_p(act), _p(w_down), _p(order), _p(offsets), _p(tiles), _p(n_tiles), _p(wts), pairs, e, ff, n,
                                0 if scale_input else 1, _p(parts), _DT[h.dtype], _DT[parts.dtype], tile_rows, s), "experts, down")
-        if top > 1:
+        if more:
+            self.launches += 1
+            gate = logits[:, outputs:] if shared_gated else None
+            _check(lib.sb_moe_combine_more(_p(parts), _p(idx), _p(wts), e, _p(h), h.stride(0), _p(shared), _p(gate), logits.stride(0), top, t, n,
+                                           _p(out), _DT[out.dtype], s), "sum over a token's experts, identity and shared expert")
+        elif top > 1:
             self.launches += 1
             _check(lib.sb_moe_combine(_p(parts), top, t, n, _p(out), _DT[out.dtype], s), "sum over a token's experts")
 

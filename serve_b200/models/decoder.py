@@ -11,7 +11,7 @@ from __future__ import annotations
 from typing import Dict, List, Optional
 
 from ..config.spec import ModelSpec
-from ..parts.base import CacheNeed, TensorDecl, build_part
+from ..parts.base import CacheNeed, TensorDecl, build_part, plain_delta
 
 
 class DecoderModel:
@@ -104,7 +104,7 @@ class DecoderModel:
         while i < n:
             run = runs.get(i) if runs else None
             if run is not None and self.rt.kernels.layer_run_takes(run[1], ctx):
-                x, pending = self.rt.kernels.layer_run(run[1], x, pending, ctx)
+                x, pending = self.rt.kernels.layer_run(run[1], x, plain_delta(pending), ctx)
                 i = run[0]
                 continue
             x, pending = self.blocks[self.schedule[i].layer].forward(x, pending, ctx, cache_views[i])

@@ -56,6 +56,7 @@ class CacheNeed:
     chunk: Optional[int] = None
     states: Tuple[Tuple[str, Tuple[int, ...]], ...] = ()
     shared_kv: bool = False      # keys and values are the same cached rows: one tensor serves as both
+    keep_first: int = 0          # with a window: the sequence's first ``keep_first`` keys stay readable for good
 
     @property
     def has_pages(self) -> bool:
@@ -63,7 +64,8 @@ class CacheNeed:
 
     def group_key(self) -> Tuple:
         """Executions with equal keys share page geometry, a pool and block tables."""
-        return (self.kv_heads, self.head_dim, self.window, self.chunk) + (("shared_kv",) if self.shared_kv else ())
+        return ((self.kv_heads, self.head_dim, self.window, self.chunk) + (("shared_kv",) if self.shared_kv else ())
+                + (("keep_first", self.keep_first) if self.keep_first else ()))
 
     @staticmethod
     def merged(needs: "List[Tuple[str, Optional[CacheNeed]]]") -> "Optional[CacheNeed]":
@@ -82,7 +84,7 @@ class CacheNeed:
         if not paged and not states:
             return None
         p = paged[0] if paged else CacheNeed()
-        return CacheNeed(p.kv_heads, p.head_dim, p.window, None, p.chunk, tuple(states), p.shared_kv)
+        return CacheNeed(p.kv_heads, p.head_dim, p.window, None, p.chunk, tuple(states), p.shared_kv, p.keep_first)
 
 
 class Part:
@@ -140,6 +142,24 @@ class FeedForward(Part):
         raise NotImplementedError
 
 
+class DeferredNorm:
+    """A sub-layer's output ``a`` that still has to go through a norm of its own before it joins the residual stream
+    (an arrangement with norms after its sub-layers hands these on as the pending delta). A norm that can apply
+    ``norm`` inside its own kernel takes the pair as it is; any other asks for ``plain()``, the normalised delta as a
+    float32 tensor."""
+
+    def __init__(self, a, norm):
+        self.a, self.norm = a, norm
+
+    def plain(self):
+        return self.norm.apply(self.a)
+
+
+def plain_delta(delta):
+    """A pending delta as a tensor (or None), whatever form it was handed on in."""
+    return delta.plain() if isinstance(delta, DeferredNorm) else delta
+
+
 class Norm(Part):
     def forward(self, x, delta, ctx):
         """x (float32 residual, updated in place with ``delta`` if given) -> normalised activations."""
@@ -147,6 +167,10 @@ class Norm(Part):
 
     def forward_rows(self, x, delta, rows, ctx):
         """As forward, but only for the rows listed (no update of x)."""
+        raise NotImplementedError
+
+    def apply(self, a):
+        """The norm of activations that are not the residual stream (a sub-layer's output): [T, size] -> float32 [T, size]."""
         raise NotImplementedError
 
 

@@ -7,7 +7,7 @@ inside the next norm kernel.
 """
 from __future__ import annotations
 
-from .base import Block, CacheNeed, register_part
+from .base import Block, CacheNeed, DeferredNorm, register_part
 
 
 @register_part("block", "pre_norm")
@@ -64,3 +64,28 @@ class PreNormFilteredBlock(Block):
             h = self.feed_forward_filter.forward(h, ctx, cache, prefix="feed_forward_filter.")
         f = self.feed_forward.forward(h, ctx)
         return x, f
+
+
+@register_part("block", "sandwich_norm")
+class SandwichNormBlock(Block):
+    """A norm before and a norm after each sub-layer: x = x + norm_b(mixer(norm(x))); x = x + norm_d(ffn(norm_c(x))).
+    The feed-forward half may be left out. A sub-layer's output is handed on together with its own norm (``DeferredNorm``):
+    the norm that reads the residual stream next applies it in the same kernel if it can, so no normalised delta is
+    written and read in between."""
+
+    wants = {"mixer_norm": "norm", "mixer": "mixer", "mixer_post_norm": "norm", "feed_forward_norm": "norm",
+             "feed_forward": "feed_forward", "feed_forward_post_norm": "norm"}
+    optional = ("feed_forward_norm", "feed_forward", "feed_forward_post_norm")
+
+    def __init__(self, spec, runtime, parts=None):
+        super().__init__(spec, runtime, parts)
+        if (self.feed_forward is None) != (self.feed_forward_norm is None) or (self.feed_forward is None) != (self.feed_forward_post_norm is None):
+            raise KeyError("sandwich_norm: a feed-forward comes with both of its norms, or none of the three is given")
+
+    def forward(self, x, pending, ctx, cache):
+        h = self.mixer_norm.forward(x, pending, ctx)
+        a = DeferredNorm(self.mixer.forward(h, ctx, cache), self.mixer_post_norm)
+        if self.feed_forward is None:
+            return x, a
+        h = self.feed_forward_norm.forward(x, a, ctx)
+        return x, DeferredNorm(self.feed_forward.forward(h, ctx), self.feed_forward_post_norm)

@@ -1,4 +1,5 @@
-"""Dense gated feed-forwards: down( act(gate x, up x) ), with act = silu(g) * u (SwiGLU) or a clamped form.
+"""Dense feed-forwards: gated, down( act(gate x, up x) ) with act = silu(g) * u (SwiGLU) or a clamped form, and plain,
+down( act(up x) ).
 
 Reference: serve/model.py:80-85 (w1 = gate, w3 = up, w2 = down, no biases).
 Gate and up weights are fused at load into one [2*I, hidden] matrix so that one
@@ -78,5 +79,41 @@ class GatedDense(SwiGLU):
         act = rt.empty_act((t, self.intermediate))
         rt.kernels.gate_up_activation(h, self.w_gate_up, act, self.activation, self.limit, self.alpha)
         out = rt.empty_act((t, self.hidden))
+        rt.kernels.linear(act, self.w_down, out)
+        return out
+
+
+@register_part("feed_forward", "plain_dense")
+class PlainDense(FeedForward):
+    """down(act(up h)) without a gate. params: hidden, intermediate, activation ("relu_squared" | "gelu_tanh" | "silu" | "tanh"),
+    names (up/down tensor names relative to prefix). The activation is computed in float32 and rounded once."""
+
+    ACTIVATIONS = ("relu_squared", "gelu_tanh", "silu", "tanh")
+
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        p = spec.params
+        self.hidden, self.intermediate = int(p["hidden"]), int(p["intermediate"])
+        self.activation = p.get("activation", "relu_squared")
+        if self.activation not in self.ACTIVATIONS:
+            raise ValueError(f"plain_dense: activation {self.activation!r} is not known ({', '.join(self.ACTIVATIONS)})")
+        names = p.get("names", {})
+        self.up_name, self.down_name = self.prefix + names.get("up", "up"), self.prefix + names.get("down", "down")
+        self.w_up = self.w_down = None
+
+    def kernel_needs(self):
+        return {"libraries": ["prep"]}
+
+    def tensor_decls(self):
+        return [TensorDecl(self.up_name, (self.intermediate, self.hidden)), TensorDecl(self.down_name, (self.hidden, self.intermediate))]
+
+    def load(self, tensors):
+        self.w_up, self.w_down = tensors[self.up_name].contiguous(), tensors[self.down_name].contiguous()
+
+    def forward(self, h, ctx):
+        rt = self.rt
+        act = rt.empty_act((h.shape[0], self.intermediate))
+        rt.kernels.linear_activation(h, self.w_up, act, self.activation)
+        out = rt.empty_act((h.shape[0], self.hidden))
         rt.kernels.linear(act, self.w_down, out)
         return out

@@ -1,12 +1,15 @@
 """Mixers that carry a matrix state per head from token to token instead of a cache of keys.
 
-All three keep S [dk, dv] per (request, head) in float and differ in how a token changes it:
+All of them keep S [dk, dv] per (request, head) in float and differ in how a token changes it:
 
   "lightning"    S <- decay_h S + k v^T,  o = S^T q          q, k, v = silu of their projections; decay_h fixed per head
   "mamba2"       S <- exp(-exp(A_h) dt) S + dt B x^T,  y = S^T C + D_h x      dt = softplus(dt' + bias_h); x, B, C pass a
                  short convolution and silu first; heads share B and C in groups
-  "gated_delta"  S <- g . S (a decay per row of S);  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
+  "gated_delta"  S <- g . S (a decay per row of S, or one per head);  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
                  q, k, v pass a short convolution and silu, q and k become unit vectors, q times dk^-1/2
+  "wkv"          o = (S + diag(u_h) k v^T)^T r;  S <- diag(d) S + k v^T      r, k, v, the gate and the decay each read
+                 their own blend of the token's input with the one before; d = exp(-exp(w0 + W2 tanh(W1 x_w))) per key
+                 channel; the bonus u_h counts for the current token only, and the read-out comes before the update
 
 The read-out goes through a root-mean-square norm with a gate (parts/gated_norm.py) and an output projection.
 One kernel walks the tokens of every request of the step in order (csrc/sequence_ops.cu), so a prompt cut into
@@ -144,7 +147,9 @@ class Mamba2Mixer(RecurrentMixer):
 @register_part("mixer", "gated_delta")
 class GatedDeltaMixer(RecurrentMixer):
     """params: hidden, heads, kv_heads, dim, vdim, taps, eps, rank (width of the two-step projections of the decay rate
-    and of the gate; None: whatever the weight file has)."""
+    and of the gate; None: whatever the weight file has); decay_per ("channel": a rate per row of S, dt_bias [heads * dim];
+    "head": one rate per head, dt_bias [heads]); low_rank (True: rate and gate come through two-step projections a1/a2 and
+    g1/g2; False: each is one projection of the layer's input, named "rate" and "gate"); gate ("sigmoid" | "silu")."""
 
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
@@ -154,6 +159,11 @@ class GatedDeltaMixer(RecurrentMixer):
         if self.heads % self.kv_heads:
             raise ValueError(f"heads {self.heads} is not a multiple of kv_heads {self.kv_heads}")
         self.rank = int(p["rank"]) if p.get("rank") else -1
+        self.per_head = p.get("decay_per", "channel") == "head"
+        if p.get("decay_per", "channel") not in ("channel", "head"):
+            raise ValueError(f"gated_delta: decay_per {p['decay_per']!r} is not known (channel, head)")
+        self.low_rank = bool(p.get("low_rank", True))
+        self.rate_size = self.heads if self.per_head else self.heads * self.dim
         self.qk, self.mixed_size = self.kv_heads * self.dim, self.heads * self.vdim
         seg = lambda n, c: (self.names.get(n + "_conv", n + ".conv"), c)
         self.conv = build_part("filter", PartSpec("short_conv", {
@@ -161,26 +171,36 @@ class GatedDeltaMixer(RecurrentMixer):
             "segments": [seg("q", self.qk), seg("k", self.qk), seg("v", self.mixed_size)]}, self.prefix), runtime)
         self.norm = build_part("norm", PartSpec("gated_group_rms", {
             "channels": self.mixed_size, "groups": self.heads, "eps": self.eps, "weight_size": self.vdim,
-            "weight_name": self.names.get("norm", "norm"), "gate": "sigmoid"}, self.prefix), runtime)
+            "weight_name": self.names.get("norm", "norm"), "gate": p.get("gate", "sigmoid")}, self.prefix), runtime)
+
+    def kernel_needs(self):
+        return {"libraries": ["seq"]}
 
     def tensor_decls(self):
         hid, r = self.hidden, self.rank
+        if self.low_rank:
+            two_step = [TensorDecl(self._name("a1"), (r, hid)), TensorDecl(self._name("a2"), (self.rate_size, r)),
+                        TensorDecl(self._name("g1"), (r, hid)), TensorDecl(self._name("g2"), (self.mixed_size, r))]
+        else:
+            two_step = [TensorDecl(self._name("rate"), (self.rate_size, hid)), TensorDecl(self._name("gate"), (self.mixed_size, hid))]
         return ([TensorDecl(self._name("q"), (self.qk, hid)), TensorDecl(self._name("k"), (self.qk, hid)),
-                 TensorDecl(self._name("v"), (self.mixed_size, hid)), TensorDecl(self._name("b"), (self.heads, hid)),
-                 TensorDecl(self._name("a1"), (r, hid)), TensorDecl(self._name("a2"), (self.heads * self.dim, r)),
-                 TensorDecl(self._name("g1"), (r, hid)), TensorDecl(self._name("g2"), (self.mixed_size, r)),
-                 TensorDecl(self._name("o"), (hid, self.mixed_size)),
-                 TensorDecl(self._name("A_log"), (self.heads,), role="vector", init="norm"),
-                 TensorDecl(self._name("dt_bias"), (self.heads * self.dim,), role="vector", init="norm")]
+                 TensorDecl(self._name("v"), (self.mixed_size, hid)), TensorDecl(self._name("b"), (self.heads, hid))] + two_step
+                + [TensorDecl(self._name("o"), (hid, self.mixed_size)),
+                   TensorDecl(self._name("A_log"), (self.heads,), role="vector", init="norm"),
+                   TensorDecl(self._name("dt_bias"), (self.rate_size,), role="vector", init="norm")]
                 + self.conv.tensor_decls() + self.norm.tensor_decls())
 
     def load(self, tensors):
         t = lambda n: tensors[self._name(n)]
-        if t("a1").shape[0] != t("a2").shape[1] or t("g1").shape[0] != t("g2").shape[1]:
-            raise ValueError(f"{self.prefix}: the two steps of a low-rank projection do not fit each other")
-        self.rank_a, self.rank_g = t("a1").shape[0], t("g1").shape[0]
-        self.w_in = torch.cat([t(n) for n in ("q", "k", "v", "b", "a1", "g1")], dim=0).contiguous()
-        self.w_a2, self.w_g2, self.w_o = t("a2").contiguous(), t("g2").contiguous(), t("o").contiguous()
+        if self.low_rank:
+            if t("a1").shape[0] != t("a2").shape[1] or t("g1").shape[0] != t("g2").shape[1]:
+                raise ValueError(f"{self.prefix}: the two steps of a low-rank projection do not fit each other")
+            self.rank_a, self.rank_g = t("a1").shape[0], t("g1").shape[0]
+            self.w_in = torch.cat([t(n) for n in ("q", "k", "v", "b", "a1", "g1")], dim=0).contiguous()
+            self.w_a2, self.w_g2 = t("a2").contiguous(), t("g2").contiguous()
+        else:
+            self.w_in = torch.cat([t(n) for n in ("q", "k", "v", "b", "rate", "gate")], dim=0).contiguous()
+        self.w_o = t("o").contiguous()
         self.a_log, self.dt_bias = t("A_log").contiguous(), t("dt_bias").contiguous()
         self.conv.load(tensors)
         self.norm.load(tensors)
@@ -192,16 +212,82 @@ class GatedDeltaMixer(RecurrentMixer):
         k = self.rt.kernels
         t, qk, hv, hd = h.shape[0], self.qk, self.mixed_size, self.heads
         n_conv = 2 * qk + hv
-        proj = self.rt.empty_act((t, n_conv + hd + self.rank_a + self.rank_g))
-        k.linear(h, self.w_in, proj)
-        qkv = self.conv.forward(proj[:, :n_conv], ctx, cache)
         at = n_conv + hd
-        rate = self.rt.empty_act((t, hd * self.dim))
-        k.linear(proj[:, at: at + self.rank_a], self.w_a2, rate)
-        gate = self.rt.empty_act((t, hv))
-        k.linear(proj[:, at + self.rank_a:], self.w_g2, gate)
+        if self.low_rank:
+            proj = self.rt.empty_act((t, at + self.rank_a + self.rank_g))
+            k.linear(h, self.w_in, proj)
+            rate = self.rt.empty_act((t, self.rate_size))
+            k.linear(proj[:, at: at + self.rank_a], self.w_a2, rate)
+            gate = self.rt.empty_act((t, hv))
+            k.linear(proj[:, at + self.rank_a:], self.w_g2, gate)
+        else:
+            proj = self.rt.empty_act((t, at + self.rate_size + hv))
+            k.linear(h, self.w_in, proj)
+            rate, gate = proj[:, at: at + self.rate_size], proj[:, at + self.rate_size:]
+        qkv = self.conv.forward(proj[:, :n_conv], ctx, cache)
         y = self._readout(t)
         k.linear_recurrence("delta", qkv[:, :qk], qkv[:, qk: 2 * qk], qkv[:, 2 * qk:], cache.states["state"], ctx, y, hd, self.kv_heads,
                             self.dim, self.vdim, aux=proj[:, n_conv: n_conv + hd], rate=rate, a_log=self.a_log, dt_bias=self.dt_bias,
-                            q_scale=1.0 / math.sqrt(self.dim))
+                            q_scale=1.0 / math.sqrt(self.dim), **({"rate_per_head": True} if self.per_head else {}))
         self.norm.forward(y, gate, out, scale)
+
+
+@register_part("mixer", "wkv")
+class WkvMixer(RecurrentMixer):
+    """params: hidden, heads, dim, eps, rank (width of the decay's two-step projection; None: whatever the weight file has).
+    Tensors: blend vectors "mu.r/k/v/g/w", projections "r", "k", "v", "g" [heads * dim, hidden], "w1" [rank, hidden], "w2"
+    [heads * dim, rank], "w0" [heads * dim], bonus "u" [heads, dim], "norm" [heads * dim], "o"."""
+
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        p = spec.params
+        self._common(p)
+        self.dim = int(p["dim"])
+        self.rank = int(p["rank"]) if p.get("rank") else -1
+        self.mixed_size = self.heads * self.dim
+        self.shift = build_part("filter", PartSpec("token_shift", {
+            "channels": self.hidden, "mixes": [self.names.get("mu." + s, "mu." + s) for s in "rkvgw"]}, self.prefix), runtime)
+        self.norm = build_part("norm", PartSpec("gated_group_rms", {
+            "channels": self.mixed_size, "groups": self.heads, "eps": self.eps, "weight_name": self.names.get("norm", "norm"),
+            "gate": "silu"}, self.prefix), runtime)
+
+    def kernel_needs(self):
+        return {"libraries": ["seq"]}
+
+    def tensor_decls(self):
+        hid, n = self.hidden, self.mixed_size
+        return ([TensorDecl(self._name(s), (n, hid)) for s in "rkvg"]
+                + [TensorDecl(self._name("w1"), (self.rank, hid)), TensorDecl(self._name("w2"), (n, self.rank)),
+                   TensorDecl(self._name("w0"), (n,), role="vector", init="norm"),
+                   TensorDecl(self._name("u"), (self.heads, self.dim), role="vector", init="normal"),
+                   TensorDecl(self._name("o"), (hid, n))]
+                + self.shift.tensor_decls() + self.norm.tensor_decls())
+
+    def load(self, tensors):
+        t = lambda n: tensors[self._name(n)]
+        if t("w1").shape[0] != t("w2").shape[1]:
+            raise ValueError(f"{self.prefix}: the two steps of the decay's projection do not fit each other")
+        self.w_rkvg = torch.stack([t(s) for s in "rkvg"]).contiguous()
+        self.w1, self.w2, self.w_o = t("w1").contiguous(), t("w2").contiguous(), t("o").contiguous()
+        self.w0, self.bonus = t("w0").float().contiguous(), t("u").float().reshape(-1).contiguous()
+        self.shift.load(tensors)
+        self.norm.load(tensors)
+
+    def cache_need(self):
+        return CacheNeed.merged([("", CacheNeed(states=(("state", (self.heads, self.dim, self.dim)),))), ("", self.shift.cache_need())])
+
+    def mix_into(self, h, ctx, cache, out, scale: float = 1.0):
+        k = self.rt.kernels
+        t, n = h.shape[0], self.mixed_size
+        blends = self.shift.forward(h, ctx, cache)                      # [5, T, hidden]: for r, k, v, the gate and the decay
+        proj = self.rt.empty_act((t, 4, n))
+        k.linear_batched(blends[:4].transpose(0, 1), self.w_rkvg, proj)
+        low = self.rt.empty_act((t, self.w1.shape[0]))
+        k.linear(blends[4], self.w1, low)
+        k.activation(low, low, "tanh")
+        rate = torch.empty((t, n), dtype=torch.float32, device=h.device)
+        k.linear(low, self.w2, rate)
+        y = self._readout(t)
+        k.linear_recurrence("wkv", proj[:, 0], proj[:, 1], proj[:, 2], cache.states["state"], ctx, y, self.heads, self.heads, self.dim,
+                            self.dim, rate=rate, dt_bias=self.w0, bonus=self.bonus)
+        self.norm.forward(y, proj[:, 3], out, scale)

@@ -8,7 +8,7 @@ weight is taken in float32 before the single rounding to the activation dtype.
 """
 from __future__ import annotations
 
-from .base import Norm, TensorDecl, register_part
+from .base import DeferredNorm, Norm, TensorDecl, plain_delta, register_part
 
 
 @register_part("norm", "rms")
@@ -34,12 +34,12 @@ class RMSNorm(Norm):
 
     def forward(self, x, delta, ctx):
         out = self.rt.empty_act((x.shape[0], self.size))
-        self.rt.kernels.add_rmsnorm(x, delta, self.weight, self.eps, out)
+        self.rt.kernels.add_rmsnorm(x, plain_delta(delta), self.weight, self.eps, out)
         return out
 
     def forward_rows(self, x, delta, rows, ctx):
         out = self.rt.empty_act((rows.shape[0], self.size))
-        self.rt.kernels.add_rmsnorm_rows(x, delta, rows, self.weight, self.eps, out)
+        self.rt.kernels.add_rmsnorm_rows(x, plain_delta(delta), rows, self.weight, self.eps, out)
         return out
 
 
@@ -53,10 +53,67 @@ class LayerNorm(RMSNorm):
 
     def forward(self, x, delta, ctx):
         out = self.rt.empty_act((x.shape[0], self.size))
-        self.rt.kernels.add_layernorm(x, delta, self.weight, self.eps, out)
+        self.rt.kernels.add_layernorm(x, plain_delta(delta), self.weight, self.eps, out)
         return out
 
     def forward_rows(self, x, delta, rows, ctx):
         out = self.rt.empty_act((rows.shape[0], self.size))
-        self.rt.kernels.add_layernorm_rows(x, delta, rows, self.weight, self.eps, out)
+        self.rt.kernels.add_layernorm_rows(x, plain_delta(delta), rows, self.weight, self.eps, out)
+        return out
+
+
+@register_part("norm", "dynamic_tanh")
+class DynamicTanh(Norm):
+    """y = tanh(alpha * x) * weight + bias, alpha a scalar: a norm without statistics, so every element stands alone. All in
+    float32. The same fusion with the residual addition as the other norms; and because it is element-wise, the norm of
+    the sub-layer before (a ``DeferredNorm`` whose norm is another dynamic tanh) is applied in the same kernel:
+    x += tanh(alpha' a) w' + b'; y = tanh(alpha x) w + b. params: size, weight_name (bias and alpha are "<weight>.b" and
+    "<weight>.alpha")."""
+
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        self.size = int(spec.params["size"])
+        self.weight_name = self.prefix + spec.params.get("weight_name", "weight")
+        self.params = None
+
+    def kernel_needs(self):
+        return {"libraries": ["prep"]}
+
+    def tensor_decls(self):
+        return [TensorDecl(self.weight_name, (self.size,), role="vector", init="norm"),
+                TensorDecl(self.weight_name + ".b", (self.size,), role="vector", init="small"),
+                TensorDecl(self.weight_name + ".alpha", (), role="vector", init="norm")]
+
+    def load(self, tensors):
+        import torch
+
+        # weight, bias and alpha as one float vector [2 * size + 1]: one pointer for the kernel, alpha on the device
+        self.params = torch.cat([tensors[self.weight_name].float().reshape(-1), tensors[self.weight_name + ".b"].float().reshape(-1),
+                                 tensors[self.weight_name + ".alpha"].float().reshape(-1)]).contiguous()
+
+    def _split(self, delta):
+        """(tensor to add or None, the parameters of the dynamic tanh it goes through first or None)."""
+        if isinstance(delta, DeferredNorm):
+            if isinstance(delta.norm, DynamicTanh):
+                return delta.a, delta.norm.params
+            return delta.plain(), None
+        return delta, None
+
+    def forward(self, x, delta, ctx):
+        out = self.rt.empty_act((x.shape[0], self.size))
+        a, through = self._split(delta)
+        self.rt.kernels.add_dynamic_tanh(x, a, through, None, self.params, out)
+        return out
+
+    def forward_rows(self, x, delta, rows, ctx):
+        out = self.rt.empty_act((rows.shape[0], self.size))
+        a, through = self._split(delta)
+        self.rt.kernels.add_dynamic_tanh(x, a, through, rows, self.params, out)
+        return out
+
+    def apply(self, a):
+        import torch
+
+        out = torch.empty((a.shape[0], self.size), dtype=torch.float32, device=a.device)
+        self.rt.kernels.add_dynamic_tanh(None, a, None, None, self.params, out)
         return out

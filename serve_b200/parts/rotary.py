@@ -23,12 +23,15 @@ PAIRING_INTERLEAVED = 1
 def rotary_inv_freq(rotary_dim: int, theta: float, scaling=None) -> torch.Tensor:
     """float32 [rotary_dim/2] inverse frequencies, scaled per frequency if asked.
 
-    ``scaling`` is None or a mapping with factor, low_freq_factor,
-    high_freq_factor, original_max_position_embeddings.
+    ``scaling`` is None, a mapping with factor, low_freq_factor,
+    high_freq_factor, original_max_position_embeddings (the llama3 rule), or
+    {"kind": "linear", "factor": f}: every frequency divided by f.
     """
     freqs = 1.0 / (theta ** (torch.arange(0, rotary_dim, 2)[: rotary_dim // 2].float() / rotary_dim))
     if scaling is None:
         return freqs
+    if scaling.get("kind") == "linear":
+        return (freqs / float(scaling["factor"])).to(torch.float32)
     factor = float(scaling["factor"])
     low = float(scaling["low_freq_factor"])
     high = float(scaling["high_freq_factor"])

@@ -131,6 +131,90 @@ class EmuKernels:
         else:
             out.copy_((g * torch.sigmoid(g) * u).to(out.dtype))
 
+    def add_dynamic_tanh(self, x, delta, through, rows, params, out):
+        """x += [tanh(alpha' delta) w' + b'] (``through`` = [w' | b' | alpha'], or the plain delta); out = tanh(alpha x) w + b
+        with params = [w | b | alpha]; with ``rows`` only for those rows and without updating x; with x None the norm of delta."""
+        def dyt(v, par):
+            n = (par.shape[0] - 1) // 2
+            par = par.to(self.math)
+            return torch.tanh(par[2 * n] * v) * par[:n] + par[n: 2 * n]
+
+        d = None
+        if delta is not None:
+            d = delta.to(self.math)
+            if through is not None and x is not None:
+                d = dyt(d, through).to(torch.float32)
+        if x is None:
+            out.copy_(dyt(d, params).to(out.dtype))
+            return
+        if rows is not None:
+            v = x[rows.long()]
+            if d is not None:
+                v = v + d[rows.long()].to(x.dtype)
+        else:
+            if d is not None:
+                x.add_(d.to(x.dtype))
+            v = x
+        out.copy_(dyt(v.to(self.math), params).to(out.dtype))
+
+    def token_shift_mix(self, x, mu, state, ctx, out):
+        cu = ctx.cu_q.tolist()
+        for r, slot in enumerate(ctx.slots.tolist()):
+            a, b = cu[r], cu[r + 1]
+            if b == a:
+                continue
+            cur = x[a:b].to(self.math)
+            prev = torch.cat([state[slot].to(self.math), cur[:-1]], 0)
+            out[:, a:b] = (cur[None] + (prev - cur)[None] * mu.to(self.math)[:, None, :]).to(out.dtype)
+            state[slot] = cur[-1:].to(state.dtype)
+
+    def activation(self, x, out, kind):
+        v = x.to(self.math)
+        if kind == "relu_squared":
+            v = torch.relu(v) ** 2
+        elif kind == "tanh":
+            v = torch.tanh(v)
+        elif kind == "silu":
+            v = v * torch.sigmoid(v)
+        elif kind == "gelu_tanh":
+            v = 0.5 * v * (1 + torch.tanh(0.7978845608028654 * (v + 0.044715 * v ** 3)))
+        else:
+            raise ValueError(kind)
+        out.copy_(v.to(out.dtype))
+
+    def linear_activation(self, h, w, out, kind):
+        self.activation(h.to(self.math) @ w.to(self.math).T, out, kind)
+
+    def add_bias(self, x, bias):
+        x.add_(bias.to(x.dtype))
+
+    def qk_prepare(self, sums, bias, positions, token_row, heads, kv_heads, head_dim, dim, q_weight, k_weight, eps, inv_freq, rot_dims,
+                   q_out, k_cache, v_cache, block_table, page_size):
+        t, d, m = sums.shape[0], head_dim, self.math
+        x = sums.to(m)
+        if bias is not None:
+            x = x + bias.to(m)
+        x = x.view(t, heads + 2 * kv_heads, d)
+        ang = positions.to(torch.float32)[:, None] * inv_freq.to(torch.float32)[None, : rot_dims // 2]
+        cos, sin = ang.cos().to(m)[:, None, :], ang.sin().to(m)[:, None, :]
+
+        def prepare(v, n_heads, weight):
+            v = v.reshape(t, n_heads * d)
+            if weight is not None:
+                v = v * torch.rsqrt(v.pow(2).sum(-1, keepdim=True) / (n_heads * dim) + eps) * weight.to(m)
+            v = v.view(t, n_heads, d).clone()
+            half = rot_dims // 2
+            if half:
+                a, b = v[..., :half].clone(), v[..., half: rot_dims].clone()
+                v[..., :half] = a * cos - b * sin
+                v[..., half: rot_dims] = b * cos + a * sin
+            return v
+
+        q_out.copy_(prepare(x[:, :heads], heads, q_weight).reshape(t, heads * d).to(q_out.dtype))
+        if kv_heads:
+            self._write_pages(k_cache, prepare(x[:, heads: heads + kv_heads], kv_heads, k_weight), positions, token_row, block_table, page_size)
+            self._write_pages(v_cache, x[:, heads + kv_heads:], positions, token_row, block_table, page_size)
+
     def linear_batched(self, a, w, out):
         """out[:, b] = a[:, b] @ w[b]^T for every b: a [M, B, K], w [B, N, K], out [M, B, N] (views with any row strides)."""
         out.copy_(torch.einsum("mbk,bnk->mbn", a.to(self.math), w.to(self.math)).to(out.dtype))
@@ -198,7 +282,7 @@ class EmuKernels:
         out.copy_(total.to(out.dtype))
 
     def attention(self, qkv, k_cache, v_cache, block_table, cu_q, kv_len, token_row, positions, heads, kv_heads, head_dim,
-                  page_size, scale, window, out, shape, slopes=None, chunk=0, softcap=0.0, sinks=None):
+                  page_size, scale, window, out, shape, slopes=None, chunk=0, softcap=0.0, sinks=None, keep_first=0):
         d = head_dim
         g = heads // kv_heads
         cu = cu_q.tolist()
@@ -213,19 +297,22 @@ class EmuKernels:
             lo = max(0, (L - n) - window + 1) if window else 0
             if chunk:
                 lo = max(lo, ((L - n) // chunk) * chunk)
-            pages = block_table[r].long()[key_pos[lo:] // page_size]
+            keys = key_pos[lo:]
+            if window and keep_first and lo > 0:
+                keys = torch.cat([key_pos[: min(keep_first, lo)], keys])       # the first tokens stay readable behind the window
+            pages = block_table[r].long()[keys // page_size]
             assert bool((pages >= 0).all()), "attention reads a missing page"
-            k = k_cache[pages, :, key_pos[lo:] % page_size].to(self.math)
-            v = v_cache[pages, :, key_pos[lo:] % page_size].to(self.math)
+            k = k_cache[pages, :, keys % page_size].to(self.math)
+            v = v_cache[pages, :, keys % page_size].to(self.math)
             kk, vv = k.repeat_interleave(g, 1), v.repeat_interleave(g, 1)
             s = torch.einsum("thd,shd->hts", q, kk) * scale
             if softcap:
                 s = softcap * torch.tanh(s / softcap)       # before any distance bias
             qp = torch.arange(L - n, L, device=qkv.device)[:, None]
-            kp = key_pos[lo:][None, :]
+            kp = keys[None, :]
             mask = kp > qp
             if window:
-                mask = mask | (kp <= qp - window)
+                mask = mask | ((kp <= qp - window) & (kp >= keep_first))
             if chunk:
                 mask = mask | (kp < (qp // chunk) * chunk)
             if slopes is not None:
@@ -262,7 +349,7 @@ class EmuKernels:
                 state[slot] = seq[-k:].to(state.dtype)
 
     def linear_recurrence(self, mode, q, k, v, state, ctx, out, heads, qk_heads, dk, dv, aux=None, rate=None, decay=None,
-                          a_log=None, dt_bias=None, d_skip=None, q_scale=1.0):
+                          a_log=None, dt_bias=None, d_skip=None, q_scale=1.0, rate_per_head=False, bonus=None):
         m = self.math
         f = torch.nn.functional
         cu = ctx.cu_q.tolist()
@@ -282,13 +369,23 @@ class EmuKernels:
                 dt = f.softplus(aux[a:b, :heads].to(m) + dt_bias.to(m), threshold=20.0)
                 dec = torch.exp(-torch.exp(a_log.to(m)) * dt)[:, :, None].expand(n, heads, dk)
                 u_scale = dt
+            elif mode == "wkv":
+                dec = torch.exp(-torch.exp(rate[a:b, : heads * dk].to(m) + dt_bias.to(m))).reshape(n, heads, dk)
+                extra = bonus.to(m).reshape(heads, dk)
             else:
                 qq = qq / torch.sqrt((qq * qq).sum(-1, keepdim=True) + 1e-6) * q_scale
                 kk = kk / torch.sqrt((kk * kk).sum(-1, keepdim=True) + 1e-6)
-                rr = f.softplus(rate[a:b, : heads * dk].to(m) + dt_bias.to(m), threshold=20.0).reshape(n, heads, dk)
+                cols = heads if rate_per_head else heads * dk
+                rr = f.softplus(rate[a:b, :cols].to(m) + dt_bias.to(m), threshold=20.0).reshape(n, heads, -1).expand(n, heads, dk)
                 dec = torch.exp(-torch.exp(a_log.to(m))[None, :, None] * rr)
                 beta = torch.sigmoid(aux[a:b, :heads].to(m))
             for i in range(n):
+                if mode == "wkv":
+                    # the read-out sees the state before this token, and this token's own k v^T times the bonus
+                    o = torch.einsum("hkv,hk->hv", s, qq[i]) + (extra * kk[i] * qq[i]).sum(-1, keepdim=True) * vv[i]
+                    s = s * dec[i][:, :, None] + kk[i][:, :, None] * vv[i][:, None, :]
+                    out[a + i] = o.reshape(-1).to(out.dtype)
+                    continue
                 s = s * dec[i][:, :, None]
                 if mode == "delta":
                     u = beta[i][:, None] * (vv[i] - torch.einsum("hkv,hk->hv", s, kk[i]))
@@ -335,20 +432,32 @@ class EmuKernels:
         v_cache[pages, :, pos % page_size] = vv.to(v_cache.dtype)
 
     def routed_experts(self, h, logits, w_gate_up, w_down, top, out, score="sigmoid", renormalise=False, scale_input=True,
-                       activation="clamped_swish", limit=0.0, alpha=1.702):
+                       activation="clamped_swish", limit=0.0, alpha=1.702, outputs=None, choice_bias=None, renormalise_eps=0.0,
+                       shared=None, shared_gated=False):
         m = self.math
-        z = logits.to(torch.float32)
+        n_out = logits.shape[1] if outputs is None else outputs
+        z = logits[:, :n_out].to(torch.float32)
         scores = torch.sigmoid(z) if score == "sigmoid" else torch.softmax(z, -1)
-        idx = torch.topk(z, top, dim=-1).indices                 # by logit: scores of large logits round to ties
+        if choice_bias is not None:
+            idx = torch.topk(scores + choice_bias.to(torch.float32), top, dim=-1).indices
+        else:
+            idx = torch.topk(z, top, dim=-1).indices             # by logit: scores of large logits round to ties
         wts = torch.gather(scores, 1, idx)
         if renormalise:
-            wts = wts / wts.sum(-1, keepdim=True)
+            wts = wts / (wts.sum(-1, keepdim=True) + renormalise_eps)
         ff = w_down.shape[2]
+        n_real = w_down.shape[0]
         total = torch.zeros((h.shape[0], w_down.shape[1]), dtype=m, device=h.device)
+        if shared is not None:
+            g = torch.sigmoid(logits[:, n_out: n_out + 1].to(m)) if shared_gated else 1.0
+            total += g * shared.to(m)
         for slot in range(top):
             for e in idx[:, slot].unique().tolist():
                 rows = (idx[:, slot] == e).nonzero().flatten()
                 w = wts[rows, slot].to(m)[:, None]
+                if e >= n_real:                                  # an identity expert: the token's input itself
+                    total[rows] += h[rows].to(m) * w
+                    continue
                 gu = h[rows].to(m) @ w_gate_up[e].to(m).T
                 if scale_input:
                     gu = gu * w

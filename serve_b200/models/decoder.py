@@ -62,6 +62,10 @@ class DecoderModel:
                 needs.append(None)
             else:
                 needs.append(self.blocks[e.layer].cache_need())
+        # an execution that reads another's pages looks at them through a mask of its own: the owner keeps what both need
+        for e in self.schedule:
+            if e.cache_of is not None and needs[e.cache_of] is not None:
+                needs[e.cache_of] = needs[e.cache_of].covering(self.blocks[e.layer].cache_need())
         return needs
 
     # ---- forward -------------------------------------------------------

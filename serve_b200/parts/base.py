@@ -67,6 +67,19 @@ class CacheNeed:
         return ((self.kv_heads, self.head_dim, self.window, self.chunk) + (("shared_kv",) if self.shared_kv else ())
                 + (("keep_first", self.keep_first) if self.keep_first else ()))
 
+    def covering(self, reader: "Optional[CacheNeed]") -> "CacheNeed":
+        """This need, widened so that ``reader`` (the need of another execution that reads the same pages with a mask of
+        its own) finds every key it may look at: the longer window (none, if either has none), the larger count of kept
+        first keys, and a block of positions only if both read the same one."""
+        if reader is None or not reader.has_pages:
+            return self
+        if (reader.kv_heads, reader.head_dim, reader.shared_kv) != (self.kv_heads, self.head_dim, self.shared_kv):
+            raise ValueError("an execution that reads another's pages must have its page geometry")
+        window = None if self.window is None or reader.window is None else max(self.window, reader.window)
+        chunk = self.chunk if self.chunk == reader.chunk else None
+        keep = max(self.keep_first, reader.keep_first) if window is not None else 0
+        return CacheNeed(self.kv_heads, self.head_dim, window, self.state_shape, chunk, self.states, self.shared_kv, keep)
+
     @staticmethod
     def merged(needs: "List[Tuple[str, Optional[CacheNeed]]]") -> "Optional[CacheNeed]":
         """One need out of those of several parts of a layer, each with the prefix its state names get. At most

@@ -77,6 +77,11 @@ def wkv_mixer(h, w, p, m, eps):
     return y @ w[p + "o"].T
 
 
+def _rot_factor(m) -> float:
+    scaling = m["rot"].get("scaling")
+    return float(scaling["factor"]) if scaling else 1.0
+
+
 def attention_keys_values(h, w, p, m, eps):
     """What an attention layer caches: keys after norm and rotation [T, G, dim], values [T, G, vdim]."""
     g, dim, vdim = m["kv_heads"], m["dim"], m["vdim"]
@@ -84,7 +89,7 @@ def attention_keys_values(h, w, p, m, eps):
     k = h @ w[p + "k"].T + w[p + "k.b"]
     v = h @ w[p + "v"].T + w[p + "v.b"]
     k = unit_rms(k, eps) * w[p + "k.norm"]
-    k = rotate_half_layout(k.view(t, g, dim), m["rot"]["base"], m["rot"]["dims"], m["rot"]["scaling"]["factor"])
+    k = rotate_half_layout(k.view(t, g, dim), m["rot"]["base"], m["rot"]["dims"], _rot_factor(m))
     return k, v.view(t, g, vdim)
 
 
@@ -94,8 +99,8 @@ def attention_mixer(h, w, p, m, eps, k, v):
     t = h.shape[0]
     q = h @ w[p + "q"].T + w[p + "q.b"]
     q = unit_rms(q, eps) * w[p + "q.norm"]
-    q = rotate_half_layout(q.view(t, heads, dim), m["rot"]["base"], m["rot"]["dims"], m["rot"]["scaling"]["factor"])
-    size, keep = m["mask"]["size"], m["mask"]["keep_first"]
+    q = rotate_half_layout(q.view(t, heads, dim), m["rot"]["base"], m["rot"]["dims"], _rot_factor(m))
+    size, keep = m["mask"]["size"], m["mask"].get("keep_first") or 0
     allowed = torch.tensor([[visible(i, j, size, keep) for j in range(t)] for i in range(t)])
     out = torch.zeros(t, heads, vdim, dtype=h.dtype)
     for n in range(heads):
@@ -179,7 +184,7 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: List[int], dtype=torc
     """Logits [T, vocab] of one sequence. ``layers_out``: a list that receives the residual stream after every layer."""
     w = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in w.items()}
     eps = cfg["norm"]["eps"]
-    x = w["embed"][torch.tensor(tokens)] * cfg["embedding"]["scale"]
+    x = w["embed"][torch.tensor(tokens)] * (cfg["embedding"]["scale"] if cfg.get("embedding") else 1.0)
     kept = {}
     for i, layer in enumerate(cfg["layers"]):
         p, m = f"l{i}.", layer["mixer"]
@@ -250,7 +255,7 @@ def tensor_shapes(cfg: dict) -> Dict[str, tuple]:
             r = f["router"]
             for e in range(r["experts"]):
                 out[f"{q}e{e}.gate"], out[f"{q}e{e}.up"], out[f"{q}e{e}.down"] = (f["expert"]["ff"], width), (f["expert"]["ff"], width), (width, f["expert"]["ff"])
-            n = r["experts"] + r.get("identity", 0)
+            n = r["experts"] + (r.get("identity") or 0)
             out[q + "router"], out[q + "correction"] = (n, width), (n,)
             if f.get("shared") is not None:
                 sf = f["shared"]["ff"]

@@ -11,7 +11,7 @@ of three: the way the reference's own benchmark times its generate()); ``prefill
 compares the decode step with the bytes it has to read (every weight once, and the cache of the live requests).
 The weights (2.47 GB) are larger than the L2 cache, so no flush is needed between steps.
 
-``--design rogisun`` (or ``bapavik``) is another measurement altogether and leaves the line above as it is: prefill and decode
+``--design rogisun`` (or ``bapavik``, ``lilunex``) is another measurement altogether and leaves the line above as it is: prefill and decode
 throughput of the Rogisun decoder (three layers, one of each mixer, routed experts) at layer sizes of real models,
 beside a Llama decoder of equal width, depth and active feed-forward size, each with the device time of every kernel
 of one prompt step and one decoding step; it prints its own JSON line (see design_bench).
@@ -367,7 +367,24 @@ def bapavik_at(width: int, vocab: int = 32000):
                              "layers": layers, "max_position": CONTEXT})
 
 
-DESIGNS = {"rogisun": rogisun_at, "bapavik": bapavik_at}
+def lilunex_at(width: int, vocab: int = 32000):
+    """A Lilunex configuration with layers of a real model's sizes: a wkv layer (heads of 64) with experts (identity outputs and a
+    gated shared expert), attention (heads of 128, a window of 1,024 keys that keeps the first four, a sink) with a dense
+    feed-forward, a gated delta layer (heads of 128) with experts."""
+    from serve_b200.config import config_from_dict
+
+    heads, experts, top, ff = DESIGN_SIZES[str(width)]
+    moe = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "identity": 4, "top": top}, "shared": {"ff": ff}}
+    att = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": 1024, "keep_first": 4},
+           "rot": {"base": 500000.0, "dims": 64, "scaling": {"factor": 4.0}}}
+    layers = [{"type": "wkv", "mixer": {"heads": width // 64, "dim": 64, "rank": 64}, "mlp": moe},
+              {"type": "attention", "mixer": att, "mlp": {"kind": "dense", "ff": top * ff}},
+              {"type": "delta", "mixer": {"heads": heads, "kv_heads": max(1, heads // 2), "dim": 128, "vdim": 128, "conv": 4}, "mlp": moe}]
+    return config_from_dict({"architecture": "Lilunex", "width": width, "vocab": vocab, "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
+                             "layers": layers, "max_position": CONTEXT})
+
+
+DESIGNS = {"rogisun": rogisun_at, "bapavik": bapavik_at, "lilunex": lilunex_at}
 
 
 def kernel_times(eng, entries, end):
@@ -414,7 +431,7 @@ def prefill_many(eng, vocab, requests, each, reps=5, seed=11):
 
 def design_bench(args):
     """Prefill (one prompt of 2,048 tokens) and decode (batch 8 after 2,048-token prompts, from CUDA graphs) of the named design
-    (Rogisun or Bapavik) and of the Llama decoder of equal size, at each width asked for, bfloat16, random weights; CUDA events on the stream, the
+    (Rogisun, Bapavik or Lilunex) and of the Llama decoder of equal size, at each width asked for, bfloat16, random weights; CUDA events on the stream, the
     weights alone exceed the L2 cache. Prints one JSON line: per width and design the two rates, the rate of a step of 8 prompts
     of 256 tokens (the same tokens side by side: what a recurrence walks in turn for one prompt it walks at once for eight),
     and the kernels of one prompt step and one (eager) decoding step with their device times."""

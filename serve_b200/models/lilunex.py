@@ -23,7 +23,8 @@ ROUTER_SUM_EPS = 1e-20        # added to the sum the chosen experts' scores are 
 
 def _mixer_spec(kind: str, m: dict, width: int, eps: float, prefix: str) -> PartSpec:
     if kind == "wkv":
-        return PartSpec("wkv", {"hidden": width, "heads": m["heads"], "dim": m["dim"], "eps": eps}, prefix)
+        # (the width of the decay's two-step projection is the weight file's; a configuration may name it, for random weights)
+        return PartSpec("wkv", {"hidden": width, "heads": m["heads"], "dim": m["dim"], "eps": eps, "rank": m.get("rank")}, prefix)
     if kind == "delta":
         return PartSpec("gated_delta", {
             "hidden": width, "heads": m["heads"], "kv_heads": m["kv_heads"], "dim": m["dim"], "vdim": m["vdim"], "taps": m["conv"],

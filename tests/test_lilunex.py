@@ -392,7 +392,8 @@ def _sees(m, query, key):
 def _edge_case(backend, m, key, query, cuts, page=8):
     cfg = _single("attention", m)
     x = _stand_out(64, sum(cuts), key, query)
-    got, want, w = _mixer_alone(backend, cfg, cuts, seed=11, x=x, tweak=_pointing(m), page=page)
+    # (the query token is minus three times the key token, so a few outputs are large: one rounding more of them counts)
+    got, want, w = _mixer_alone(backend, cfg, cuts, seed=11, x=x, tweak=_pointing(m), page=page, loose=1.5)
     # the premise: where the mask lets the query see the key, the key carries the output (without it the output is another
     # one); where it does not, the key changes nothing
     x2 = x.bfloat16().float().clone()
@@ -486,7 +487,7 @@ def test_a_state_carries_the_first_token_over_hundreds(backend, kind):
     x2 = x.bfloat16().double().clone()
     x2[0] = 0.0
     other = {"wkv": P.wkv_mixer, "delta": P.delta_mixer}[kind](x2, F64(w), "l0.mix.", m, 1e-5).float()
-    assert float((other[299] - want[299]).abs().max()) > 20 * _tol(backend, want)
+    assert float((other[299] - want[299]).abs().max()) > 10 * _tol(("emu", "float32"), want)
 
 
 # ---- feed-forwards, norm, token shift ------------------------------------------------------------------------
@@ -650,13 +651,14 @@ def test_a_model_at_the_sizes_of_a_real_layer(backend, tmp_path):
     w = make_weights(cfg, 41, RANKS["wide"])
     folder = write_model(str(tmp_path / "wide"), cfg, w, getattr(torch, backend[1]))
     reqs = {f"r{i}": helpers.random_tokens(cfg["vocab"], n, seed=50 + i) for i, n in enumerate([400, 37, 170])}
-    plain = {rid: plain_logits(w, cfg, toks)[-45:] for rid, toks in reqs.items()}
+    tail = {rid: min(45, len(toks)) for rid, toks in reqs.items()}
+    plain = {rid: plain_logits(w, cfg, toks)[-tail[rid]:] for rid, toks in reqs.items()}
     eng = make_engine(folder, backend, 64, num_pages=12, graphs=True, budget=512)
     steps = helpers.trace_mixed(reqs, live=3, seed=5, decode_tail=20, budget=256)
     with torch.inference_mode():
         got = helpers.replay(eng, steps)
     eng.kernels.check_errors()
-    got = {(rid, pos - (len(reqs[rid]) - 45)): row for (rid, pos), row in got.items() if pos >= len(reqs[rid]) - 45}
+    got = {(rid, pos - (len(reqs[rid]) - tail[rid])): row for (rid, pos), row in got.items() if pos >= len(reqs[rid]) - tail[rid]}
     assert len(got) > 60
     compare_rows(got, plain, backend)
 

@@ -116,7 +116,17 @@ struct RopeEpilogue {
   // gate/up epilogue: limit > 0 asks for the clamped activation g <- min(g, limit), u <- clamp(u, -limit, limit),
   // g * sigmoid(alpha g) * (u + 1) in place of silu(g) * u
   float act_limit, act_alpha;
+  // plain products: an activation on every output, after its rounding to bfloat16 (0: none, 1: relu squared, 2: gelu in
+  // its tanh form, 3: silu, 4: tanh)
+  int store_act;
 };
+
+__device__ __forceinline__ float plain_act(float z, int kind) {
+  if (kind == 1) { const float r = fmaxf(z, 0.f); return r * r; }
+  if (kind == 2) return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+  if (kind == 3) return z / (1.f + expf(-z));
+  return kind == 4 ? tanhf(z) : z;
+}
 
 __device__ __forceinline__ float gated_act(float g, float u, float limit, float alpha) {
   if (limit > 0.f) {
@@ -321,6 +331,8 @@ __global__ void __launch_bounds__(THREADS) gemm_tcgen05_kernel(const __grid_cons
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             __nv_bfloat162 o = __floats2bfloat162_rn(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+            if (ra.store_act)          // on the rounded product, as the unfused path stores it first
+              o = __floats2bfloat162_rn(plain_act(__low2float(o), ra.store_act), plain_act(__high2float(o), ra.store_act));
             packed[i] = *reinterpret_cast<uint32_t*>(&o);
           }
         }
@@ -524,6 +536,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS)
 #pragma unroll
           for (int i = 0; i < 16; ++i) {
             __nv_bfloat162 o = __floats2bfloat162_rn(__uint_as_float(v[2 * i]), __uint_as_float(v[2 * i + 1]));
+            if (ra.store_act)          // on the rounded product, as the unfused path stores it first
+              o = __floats2bfloat162_rn(plain_act(__low2float(o), ra.store_act), plain_act(__high2float(o), ra.store_act));
             packed[i] = *reinterpret_cast<uint32_t*>(&o);
           }
         }
@@ -714,6 +728,14 @@ SB_EXPORT int sb_gemm_tcgen05_gate_up_clamped(const void* a, const void* w, void
 }
 
 // error: device int set to 1 if a bounded wait inside the kernel ran out.
+// out [M, N] = act(a w^T), the activation (see RopeEpilogue::store_act) on the product rounded to bfloat16.
+SB_EXPORT int sb_gemm_tcgen05_act(const void* a, const void* w, void* out, int M, int N, int K, int act, int* error, cudaStream_t stream) {
+  if (act < 1 || act > 4) return SB_ERR_SHAPE;
+  RopeEpilogue ra = {};
+  ra.store_act = act;
+  return run_product(a, w, out, M, N, K, EPI_STORE, ra, error, stream);
+}
+
 SB_EXPORT int sb_gemm_tcgen05(const void* a, const void* w, void* out, int M, int N, int K, int gate_up, int* error,
                               cudaStream_t stream) {
   return run_product(a, w, out, M, N, K, gate_up ? EPI_GATE_UP : EPI_STORE, RopeEpilogue{}, error, stream);
@@ -735,7 +757,7 @@ SB_EXPORT int sb_gemm_tcgen05_qkv_rope(const void* a, const void* w, void* out, 
   if (!sb_gemm_tcgen05_qkv_rope_supports(M, K, rot, H, Hkv, D) || ps <= 0) return SB_ERR_SHAPE;
   if (!positions || !errors || (rot > 0 && (!cos_sin || ((uintptr_t)cos_sin & 7)))) return SB_ERR_ALIGN;
   if (write_cache && (!kc || !vc || !block_table || !token_row || !aligned16(kc) || !aligned16(vc))) return SB_ERR_ALIGN;
-  RopeEpilogue ra;
+  RopeEpilogue ra = {};
   ra.positions = positions;
   ra.token_row = token_row;
   ra.cos_sin = (const float2*)cos_sin;

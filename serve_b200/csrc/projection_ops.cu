@@ -303,6 +303,43 @@ __global__ void __launch_bounds__(256) dynamic_tanh_kernel(float* __restrict__ x
   }
 }
 
+// The same, four elements a thread with 16-byte (8-byte for bfloat16) loads and stores: dim a multiple of 4 and every
+// pointer aligned to 16 bytes.
+template <typename TD, typename TO>
+__global__ void __launch_bounds__(256) dynamic_tanh_vec_kernel(float* __restrict__ x, const TD* __restrict__ delta,
+                                                               const float* __restrict__ through, const int* __restrict__ rows,
+                                                               const float* __restrict__ par, TO* __restrict__ out, int n_rows, int dim) {
+  const float alpha = par[2 * dim];
+  const float alpha_d = through ? through[2 * dim] : 0.f;
+  const int dim4 = dim >> 2;
+  const size_t total4 = (size_t)n_rows * dim4;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total4; i += (size_t)gridDim.x * blockDim.x) {
+    const int r = (int)(i / dim4), c = (int)(i - (size_t)r * dim4) * 4;
+    const size_t src = (size_t)(rows ? rows[r] : r) * dim + c;
+    float4 v;
+    if (x) {
+      v = *reinterpret_cast<const float4*>(x + src);
+      if (delta) {
+        float4 d = load4f<TD>(delta + src);
+        if (through) {
+          const float4 w = *reinterpret_cast<const float4*>(through + c), b = *reinterpret_cast<const float4*>(through + dim + c);
+          d.x = tanhf(alpha_d * d.x) * w.x + b.x; d.y = tanhf(alpha_d * d.y) * w.y + b.y;
+          d.z = tanhf(alpha_d * d.z) * w.z + b.z; d.w = tanhf(alpha_d * d.w) * w.w + b.w;
+        }
+        v.x += d.x; v.y += d.y; v.z += d.z; v.w += d.w;
+        if (!rows) *reinterpret_cast<float4*>(x + src) = v;
+      }
+    } else {
+      v = load4f<TD>(delta + src);
+    }
+    const float4 w = *reinterpret_cast<const float4*>(par + c), b = *reinterpret_cast<const float4*>(par + dim + c);
+    float4 o;
+    o.x = tanhf(alpha * v.x) * w.x + b.x; o.y = tanhf(alpha * v.y) * w.y + b.y;
+    o.z = tanhf(alpha * v.z) * w.z + b.z; o.w = tanhf(alpha * v.w) * w.w + b.w;
+    store4f<TO>(out + (size_t)r * dim + c, o);
+  }
+}
+
 // ------------------------------------------------------------------------------------- activations, bias, on their own
 constexpr int ACT_RELU_SQUARED = 0, ACT_GELU_TANH = 1, ACT_SILU = 2, ACT_TANH = 3;
 
@@ -341,12 +378,15 @@ __global__ void __launch_bounds__(256) qk_prepare_kernel(
     float eps, const float* __restrict__ inv_freq, int rot, T* __restrict__ q_out, int q_stride, T* __restrict__ kc, T* __restrict__ vc,
     const int* __restrict__ block_table, int bt_width, int ps, int num_pages, int* __restrict__ errors) {
   __shared__ float red[32];
+  extern __shared__ float cs_table[];       // [half] cosines, [half] sines of this token's angles
   const int t = blockIdx.x;
   const float* row = sums + (size_t)t * stride;
   const int nq = H * D, nk = G * D, half = rot >> 1;
   const int pos = positions[t];
+  for (int j = threadIdx.x; j < half; j += blockDim.x) sincosf((float)pos * inv_freq[j], &cs_table[half + j], &cs_table[j]);
   auto val = [&](int i) { return row[i] + (bias ? bias[i] : 0.f); };
   float inv_q = 1.f, inv_k = 1.f;
+  __syncthreads();                          // the table is whole
   if (q_weight != nullptr) {
     float sq = 0.f;
     for (int i = threadIdx.x; i < nq; i += blockDim.x) { const float v = val(i); sq += v * v; }
@@ -363,8 +403,7 @@ __global__ void __launch_bounds__(256) qk_prepare_kernel(
     const float v = normed(d);
     if (d >= rot) return v;
     const int j = d < half ? d : d - half;
-    float sn, cs;
-    sincosf((float)pos * inv_freq[j], &sn, &cs);
+    const float cs = cs_table[j], sn = cs_table[half + j];
     const float other = normed(d < half ? d + half : d - half);
     return d < half ? v * cs - other * sn : v * cs + other * sn;
   };
@@ -393,9 +432,12 @@ __global__ void __launch_bounds__(256) qk_prepare_kernel(
 template <typename TD, typename TO>
 static int launch_dynamic_tanh(float* x, const void* delta, const float* through, const int* rows, const float* par, void* out, int n_rows,
                                int dim, cudaStream_t stream) {
-  const size_t total = (size_t)n_rows * dim, want = (total + 255) / 256;
+  const bool vec = dim % 4 == 0 && (!x || aligned16(x)) && (!delta || aligned16(delta)) && (!through || aligned16(through)) &&
+                   aligned16(par) && aligned16(out);
+  const size_t total = (size_t)n_rows * (vec ? dim / 4 : dim), want = (total + 255) / 256;
   const int blocks = (int)(want < (size_t)sm_count() * 16 ? want : (size_t)sm_count() * 16);
-  dynamic_tanh_kernel<TD, TO><<<blocks, 256, 0, stream>>>(x, (const TD*)delta, through, rows, par, (TO*)out, n_rows, dim);
+  if (vec) dynamic_tanh_vec_kernel<TD, TO><<<blocks, 256, 0, stream>>>(x, (const TD*)delta, through, rows, par, (TO*)out, n_rows, dim);
+  else dynamic_tanh_kernel<TD, TO><<<blocks, 256, 0, stream>>>(x, (const TD*)delta, through, rows, par, (TO*)out, n_rows, dim);
   SB_LAUNCH_CHECK();
   return 0;
 }
@@ -453,12 +495,14 @@ SB_EXPORT int sb_qk_prepare(const float* sums, int stride, const float* bias, co
   if (H <= 0 || G < 0 || D <= 0 || dim <= 0 || dim > D || stride < (H + 2 * G) * D || q_stride < H * D) return SB_ERR_SHAPE;
   if (rot < 0 || (rot & 1) || rot > dim || (rot > 0 && !inv_freq)) return SB_ERR_SHAPE;
   if (G > 0 && (ps <= 0 || bt_width <= 0 || !kc || !vc || !errors)) return SB_ERR_SHAPE;
+  const size_t smem = (size_t)(rot > 0 ? rot : 2) * sizeof(float);
+  if (smem > 40 * 1024) return SB_ERR_LIMIT;
   if (dtype == SB_DTYPE_F32)
-    qk_prepare_kernel<float><<<n_tokens, 256, 0, stream>>>(sums, stride, bias, positions, token_row, H, G, D, dim, q_weight, k_weight, eps,
+    qk_prepare_kernel<float><<<n_tokens, 256, smem, stream>>>(sums, stride, bias, positions, token_row, H, G, D, dim, q_weight, k_weight, eps,
                                                             inv_freq, rot, (float*)q_out, q_stride, (float*)kc, (float*)vc, block_table,
                                                             bt_width, ps, num_pages, errors);
   else if (dtype == SB_DTYPE_BF16)
-    qk_prepare_kernel<__nv_bfloat16><<<n_tokens, 256, 0, stream>>>(sums, stride, bias, positions, token_row, H, G, D, dim, q_weight, k_weight,
+    qk_prepare_kernel<__nv_bfloat16><<<n_tokens, 256, smem, stream>>>(sums, stride, bias, positions, token_row, H, G, D, dim, q_weight, k_weight,
                                                                     eps, inv_freq, rot, (__nv_bfloat16*)q_out, q_stride, (__nv_bfloat16*)kc,
                                                                     (__nv_bfloat16*)vc, block_table, bt_width, ps, num_pages, errors);
   else

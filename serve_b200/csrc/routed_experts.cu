@@ -87,8 +87,10 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
 
 // As moe_route_kernel, for a router with a bias on the choice: the scores (softmax over the first E of a row's ``stride``
 // logits, or sigmoid) choose through score + bias[e], lowest index first on ties, while the weights are the scores
-// themselves, divided by (their sum + sum_eps) if asked. E counts every output the router scores; an index at or beyond
+// themselves, divided by (their sum + sum_eps) if asked. A lane holds PER_LANE outputs (E <= 32 * PER_LANE): few for the
+// usual counts, so the loops over them are short. E counts every output the router scores; an index at or beyond
 // the number of real experts means "the token itself" to the kernels after this one.
+template <int PER_LANE>
 __global__ void __launch_bounds__(128) moe_route_bias_kernel(const float* __restrict__ logits, int stride, int E, int top, int score_kind,
                                                              int renorm, float sum_eps, const float* __restrict__ bias, int n_tokens,
                                                              int* __restrict__ idx, float* __restrict__ wts) {
@@ -96,10 +98,10 @@ __global__ void __launch_bounds__(128) moe_route_bias_kernel(const float* __rest
   const int t = blockIdx.x * 4 + (threadIdx.x >> 5);
   if (t >= n_tokens) return;
   const float* z = logits + (size_t)t * stride;
-  float score[ROUTE_PER_LANE], pick[ROUTE_PER_LANE];
+  float score[PER_LANE], pick[PER_LANE];
   float zmax = -INFINITY;
 #pragma unroll
-  for (int u = 0; u < ROUTE_PER_LANE; ++u) {
+  for (int u = 0; u < PER_LANE; ++u) {
     const int e = lane + 32 * u;
     score[u] = e < E ? z[e] : -INFINITY;
     zmax = fmaxf(zmax, score[u]);
@@ -109,19 +111,19 @@ __global__ void __launch_bounds__(128) moe_route_bias_kernel(const float* __rest
     for (int o = 16; o > 0; o >>= 1) zmax = fmaxf(zmax, __shfl_xor_sync(0xffffffffu, zmax, o));
     float part = 0.f;
 #pragma unroll
-    for (int u = 0; u < ROUTE_PER_LANE; ++u)
+    for (int u = 0; u < PER_LANE; ++u)
       if (lane + 32 * u < E) { score[u] = expf(score[u] - zmax); part += score[u]; }
     const float denom = warp_sum(part);
 #pragma unroll
-    for (int u = 0; u < ROUTE_PER_LANE; ++u)
+    for (int u = 0; u < PER_LANE; ++u)
       if (lane + 32 * u < E) score[u] /= denom;
   } else {
 #pragma unroll
-    for (int u = 0; u < ROUTE_PER_LANE; ++u)
+    for (int u = 0; u < PER_LANE; ++u)
       if (lane + 32 * u < E) score[u] = sigmoid_f(score[u]);
   }
 #pragma unroll
-  for (int u = 0; u < ROUTE_PER_LANE; ++u) {
+  for (int u = 0; u < PER_LANE; ++u) {
     const int e = lane + 32 * u;
     pick[u] = e < E ? score[u] + (bias ? bias[e] : 0.f) : -INFINITY;
   }
@@ -131,7 +133,7 @@ __global__ void __launch_bounds__(128) moe_route_bias_kernel(const float* __rest
     float m = -INFINITY, sc = 0.f;
     int arg = 0x7fffffff;
 #pragma unroll
-    for (int u = 0; u < ROUTE_PER_LANE; ++u) {
+    for (int u = 0; u < PER_LANE; ++u) {
       const int e = lane + 32 * u;
       if (e < E && pick[u] != -INFINITY && (pick[u] > m || (pick[u] == m && e < arg))) { m = pick[u]; arg = e; sc = score[u]; }
     }
@@ -144,7 +146,7 @@ __global__ void __launch_bounds__(128) moe_route_bias_kernel(const float* __rest
     }
     if (arg != 0x7fffffff && (arg & 31) == lane) {
 #pragma unroll
-      for (int u = 0; u < ROUTE_PER_LANE; ++u)
+      for (int u = 0; u < PER_LANE; ++u)
         if (u == (arg >> 5)) pick[u] = -INFINITY;    // taken
     }
     total += sc;
@@ -599,24 +601,66 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const float* __restric
 // The sum over a token's choices when some of them are not experts, plus what every token gets:
 //   out[t] = sum_k ( idx[t, k] < E_real ? parts[t * top + k] : wts[t * top + k] * x[t] )  +  g_t * shared[t]
 // with g_t = sigmoid(gate[t * gate_stride]) if a gate is given, else 1; shared may be null.
-template <typename T>
+template <typename T> __device__ __forceinline__ float4 moe_load4(const T* p);
+template <> __device__ __forceinline__ float4 moe_load4<float>(const float* p) { return *reinterpret_cast<const float4*>(p); }
+template <> __device__ __forceinline__ float4 moe_load4<__nv_bfloat16>(const __nv_bfloat16* p) {
+  const uint2 u = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&u.x), b = *reinterpret_cast<const __nv_bfloat162*>(&u.y);
+  return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+}
+template <typename T> __device__ __forceinline__ void moe_store4(T* p, float4 v);
+template <> __device__ __forceinline__ void moe_store4<float>(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+template <> __device__ __forceinline__ void moe_store4<__nv_bfloat16>(__nv_bfloat16* p, float4 v) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  uint2 u;
+  u.x = *reinterpret_cast<uint32_t*>(&a);
+  u.y = *reinterpret_cast<uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(p) = u;
+}
+
+// VEC elements a thread (4: N and x_stride multiples of 4, every pointer 16-byte aligned; else 1).
+template <typename T, int VEC>
 __global__ void __launch_bounds__(256) moe_combine_more_kernel(const float* __restrict__ parts, const int* __restrict__ idx,
                                                                const float* __restrict__ wts, int E_real, const T* __restrict__ x,
                                                                int x_stride, const T* __restrict__ shared, const float* __restrict__ gate,
                                                                int gate_stride, int top, int N, long long total, T* __restrict__ out) {
+  const int nv = N / VEC;
   for (long long w = (long long)blockIdx.x * blockDim.x + threadIdx.x; w < total; w += (long long)gridDim.x * blockDim.x) {
-    const long long t = w / N;
-    const int c = (int)(w - t * N);
-    float s = 0.f;
+    const int t = (int)(w / nv);
+    const int c = (int)(w - (long long)t * nv) * VEC;
+    float s[VEC];
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) s[v] = 0.f;
     for (int k = 0; k < top; ++k) {
       const size_t pair = (size_t)t * top + k;
-      s += idx[pair] < E_real ? parts[pair * N + c] : wts[pair] * to_float(x[(size_t)t * x_stride + c]);
+      if (idx[pair] < E_real) {
+        if (VEC == 4) {
+          const float4 p4 = *reinterpret_cast<const float4*>(parts + pair * N + c);
+          s[0] += p4.x; s[1 % VEC] += p4.y; s[2 % VEC] += p4.z; s[3 % VEC] += p4.w;
+        } else {
+          s[0] += parts[pair * N + c];
+        }
+      } else {
+        const float wt = wts[pair];
+        if (VEC == 4) {
+          const float4 x4 = moe_load4<T>(x + (size_t)t * x_stride + c);
+          s[0] += wt * x4.x; s[1 % VEC] += wt * x4.y; s[2 % VEC] += wt * x4.z; s[3 % VEC] += wt * x4.w;
+        } else {
+          s[0] += wt * to_float(x[(size_t)t * x_stride + c]);
+        }
+      }
     }
     if (shared) {
       const float g = gate ? sigmoid_f(gate[(size_t)t * gate_stride]) : 1.f;
-      s += g * to_float(shared[w]);
+      if (VEC == 4) {
+        const float4 h4 = moe_load4<T>(shared + (size_t)t * N + c);
+        s[0] += g * h4.x; s[1 % VEC] += g * h4.y; s[2 % VEC] += g * h4.z; s[3 % VEC] += g * h4.w;
+      } else {
+        s[0] += g * to_float(shared[(size_t)t * N + c]);
+      }
     }
-    out[w] = from_float<T>(s);
+    if (VEC == 4) moe_store4<T>(out + (size_t)t * N + c, make_float4(s[0], s[1 % VEC], s[2 % VEC], s[3 % VEC]));
+    else out[(size_t)t * N + c] = from_float<T>(s[0]);
   }
 }
 
@@ -787,7 +831,9 @@ SB_EXPORT int sb_moe_route_bias(const float* logits, int stride, int E, int top,
   if (n_tokens <= 0) return 0;
   if (E <= 0 || top <= 0 || top > E || top > ROUTE_MAX_TOP || E > 32 * ROUTE_PER_LANE) return SB_ERR_LIMIT;
   if (stride < E) return SB_ERR_SHAPE;
-  moe_route_bias_kernel<<<(n_tokens + 3) / 4, 128, 0, stream>>>(logits, stride, E, top, score_kind, renorm, sum_eps, bias, n_tokens, idx, wts);
+  auto k = E <= 64 ? moe_route_bias_kernel<2> : E <= 128 ? moe_route_bias_kernel<4> : E <= 256 ? moe_route_bias_kernel<8>
+                                                                                               : moe_route_bias_kernel<ROUTE_PER_LANE>;
+  k<<<(n_tokens + 3) / 4, 128, 0, stream>>>(logits, stride, E, top, score_kind, renorm, sum_eps, bias, n_tokens, idx, wts);
   SB_LAUNCH_CHECK();
   return 0;
 }
@@ -800,17 +846,19 @@ SB_EXPORT int sb_moe_combine_more(const float* parts, const int* idx, const floa
                                   int dtype, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (!parts || !idx || !wts || !x || top <= 0 || x_stride < N) return SB_ERR_SHAPE;
-  const long long total = (long long)n_tokens * N;
+  const bool vec = N % 4 == 0 && x_stride % 4 == 0 && aligned16(parts) && aligned16(x) && aligned16(out) && (!shared || aligned16(shared));
+  const long long total = (long long)n_tokens * (vec ? N / 4 : N);
   const long long want = (total + 255) / 256;
-  const int blocks = (int)(want < sm_count() * 8 ? want : sm_count() * 8);
-  if (dtype == SB_DTYPE_F32)
-    moe_combine_more_kernel<float><<<blocks, 256, 0, stream>>>(parts, idx, wts, E_real, (const float*)x, x_stride, (const float*)shared, gate,
-                                                               gate_stride, top, N, total, (float*)out);
-  else if (dtype == SB_DTYPE_BF16)
-    moe_combine_more_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(parts, idx, wts, E_real, (const __nv_bfloat16*)x, x_stride,
-                                                                       (const __nv_bfloat16*)shared, gate, gate_stride, top, N, total,
-                                                                       (__nv_bfloat16*)out);
-  else return SB_ERR_DTYPE;
+  const int blocks = (int)(want < sm_count() * 16 ? want : sm_count() * 16);
+  if (dtype == SB_DTYPE_F32) {
+    auto k = vec ? moe_combine_more_kernel<float, 4> : moe_combine_more_kernel<float, 1>;
+    k<<<blocks, 256, 0, stream>>>(parts, idx, wts, E_real, (const float*)x, x_stride, (const float*)shared, gate, gate_stride, top, N, total,
+                                  (float*)out);
+  } else if (dtype == SB_DTYPE_BF16) {
+    auto k = vec ? moe_combine_more_kernel<__nv_bfloat16, 4> : moe_combine_more_kernel<__nv_bfloat16, 1>;
+    k<<<blocks, 256, 0, stream>>>(parts, idx, wts, E_real, (const __nv_bfloat16*)x, x_stride, (const __nv_bfloat16*)shared, gate, gate_stride,
+                                  top, N, total, (__nv_bfloat16*)out);
+  } else return SB_ERR_DTYPE;
   SB_LAUNCH_CHECK();
   return 0;
 }

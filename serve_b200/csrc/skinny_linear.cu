@@ -54,7 +54,17 @@ struct RopeArgs {
   // gate/up products: limit > 0 asks for the clamped activation g <- min(g, limit), u <- clamp(u, -limit, limit),
   // g * sigmoid(alpha g) * (u + 1) in place of silu(g) * u
   float act_limit, act_alpha;
+  // plain products: an activation on every output, after its rounding to the output type (0: none, 1: relu squared,
+  // 2: gelu in its tanh form, 3: silu, 4: tanh)
+  int store_act;
 };
+
+__device__ __forceinline__ float plain_act(float z, int kind) {
+  if (kind == 1) { const float r = fmaxf(z, 0.f); return r * r; }
+  if (kind == 2) return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+  if (kind == 3) return z / (1.f + expf(-z));
+  return kind == 4 ? tanhf(z) : z;
+}
 
 // MT: tiles of 16 activation rows (M <= 16*MT); HALF: only rows 0..7 of the single tile exist (M <= 8).
 // NT: tiles of 8 output columns per block (2 for very wide outputs: fewer, fatter blocks).
@@ -221,6 +231,7 @@ __global__ void __launch_bounds__(THREADS, 2) skinny_linear_kernel(const bf16* _
       }
       continue;
     }
+    if (!GU && ra.store_act) v = plain_act(to_float(from_float<OutT>(v)), ra.store_act);      // as if the product had been stored first
     out[(size_t)m * N + n] = from_float<OutT>(v);
   }
 }
@@ -242,9 +253,9 @@ inline bool wide_blocks(int N) {
 
 template <bool GU, typename OutT>
 int launch_mt(const void* a, const void* w, void* out, int M, int N, int K, cudaStream_t stream, float act_limit = 0.f,
-              float act_alpha = 1.f) {
+              float act_alpha = 1.f, int store_act = 0) {
   RopeArgs none = {};
-  none.act_limit = act_limit; none.act_alpha = act_alpha;
+  none.act_limit = act_limit; none.act_alpha = act_alpha; none.store_act = store_act;
   // A plain product with bfloat16 output is followed by the add + norm kernel (a handful of blocks). If that kernel
   // is launched ahead, it should come in when this kernel's products are done, not when they start: it would release
   // its own successor at once, and blocks of kernels two and three launches ahead would take the places of running ones.
@@ -389,6 +400,13 @@ SB_EXPORT int sb_skinny_gate_up_clamped(const void* a, const void* w, void* out,
   return launch_mt<true, bf16>(a, w, out, M, N, K, stream, limit, alpha);
 }
 
+// out [M, N] bf16 = act(a w^T), the activation (see RopeArgs::store_act) on the product rounded to bfloat16.
+SB_EXPORT int sb_skinny_linear_act(const void* a, const void* w, void* out, int M, int N, int K, int act, cudaStream_t stream) {
+  if (!sb_skinny_linear_supports(M, N, K, 0) || act < 1 || act > 4) return SB_ERR_SHAPE;
+  if (!aligned16(a) || !aligned16(w)) return SB_ERR_ALIGN;
+  return launch_mt<false, bf16>(a, w, out, M, N, K, stream, 0.f, 1.f, act);
+}
+
 // a [M,K] bf16, w [N,K] bf16 (or [2N,K] with gate_up), out [M,N] bf16 (out_dtype 1) or float (0).
 SB_EXPORT int sb_skinny_linear(const void* a, const void* w, void* out, int M, int N, int K, int out_dtype, int gate_up,
                                cudaStream_t stream) {
@@ -416,7 +434,7 @@ SB_EXPORT int sb_skinny_qkv_rope(const void* a, const void* w, void* out, int M,
   RopeArgs ra;
   ra.positions = positions; ra.token_row = token_row; ra.inv_freq = inv_freq; ra.rot = rot; ra.H = H; ra.Hkv = Hkv; ra.D = D;
   ra.kc = (bf16*)kc; ra.vc = (bf16*)vc; ra.block_table = block_table; ra.bt_width = bt_width; ra.ps = ps; ra.num_pages = num_pages;
-  ra.write_cache = write_cache; ra.errors = errors; ra.late_trigger = 0; ra.act_limit = 0.f; ra.act_alpha = 1.f;
+  ra.write_cache = write_cache; ra.errors = errors; ra.late_trigger = 0; ra.act_limit = 0.f; ra.act_alpha = 1.f; ra.store_act = 0;
   const bool wide = wide_blocks(N);
   if (M <= 8) {
     if (wide) return launch<1, true, 2, false, true, bf16>(a, w, out, M, N, K, ra, stream);

@@ -314,7 +314,22 @@ class CudaKernels:
                                               self._s()), "activation")
 
     def linear_activation(self, h, w, out, kind: str) -> None:
-        """out = act(h @ w^T): the product, then the activation in place."""
+        """out = act(h @ w^T), the activation on the product rounded to the activations' type: in bfloat16 in the epilogue of
+        the few-rows product or of the tensor-memory product where they take the sizes, else the product and then the
+        activation kernel in place."""
+        m, n, k = h.shape[0], w.shape[0], h.shape[1]
+        if (h.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and h.stride(0) == k and out.stride(0) == n and w.shape[1] == k
+                and tuple(out.shape) == (m, n)):
+            code = self._ACTIVATIONS[kind] + 1
+            if self.use_skinny_linear and self._core.sb_skinny_linear_supports(m, n, k, 0):
+                self.launches += 1
+                _check(self._core.sb_skinny_linear_act(_p(h), _p(w), _p(out), m, n, k, code, self._s()), "skinny linear with activation")
+                return
+            if self._tcgen05_worthwhile(m, n) and self._core.sb_gemm_tcgen05_supports(m, n, k, 0):
+                self.launches += 1
+                _check(self._core.sb_gemm_tcgen05_act(_p(h), _p(w), _p(out), m, n, k, code, self._wait_flag(), self._s()),
+                       "tcgen05 product with activation")
+                return
         self.linear(h, w, out)
         self.activation(out, out, kind)
 

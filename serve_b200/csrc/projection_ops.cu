@@ -370,7 +370,8 @@ __global__ void __launch_bounds__(256) add_bias_kernel(float* __restrict__ x, co
 // together) by the root mean square over their H * dim (G * dim) true elements and multiply by a float weight laid out
 // like the padded projection; rotate the first ``rot`` elements of every query and key head, element i with i + rot / 2,
 // by the angle position * inv_freq[i]; queries to q_out [T, H * D], keys and values to their page. Everything is float
-// until the one rounding at the store.
+// until the one rounding at the store. The row (with its bias) and the token's cosines and sines are kept in shared
+// memory, so the sums are read from memory once (rows of up to 200 KB).
 template <typename T>
 __global__ void __launch_bounds__(256) qk_prepare_kernel(
     const float* __restrict__ sums, int stride, const float* __restrict__ bias, const int* __restrict__ positions,
@@ -378,28 +379,30 @@ __global__ void __launch_bounds__(256) qk_prepare_kernel(
     float eps, const float* __restrict__ inv_freq, int rot, T* __restrict__ q_out, int q_stride, T* __restrict__ kc, T* __restrict__ vc,
     const int* __restrict__ block_table, int bt_width, int ps, int num_pages, int* __restrict__ errors) {
   __shared__ float red[32];
-  extern __shared__ float cs_table[];       // [half] cosines, [half] sines of this token's angles
+  extern __shared__ float dyn[];            // [half] cosines, [half] sines of this token's angles, then the token's row with its bias
   const int t = blockIdx.x;
   const float* row = sums + (size_t)t * stride;
   const int nq = H * D, nk = G * D, half = rot >> 1;
+  const int n_all = nq + 2 * nk;
+  float* cs_table = dyn;
+  float* vals = dyn + (rot > 0 ? rot : 2);
   const int pos = positions[t];
   for (int j = threadIdx.x; j < half; j += blockDim.x) sincosf((float)pos * inv_freq[j], &cs_table[half + j], &cs_table[j]);
-  auto val = [&](int i) { return row[i] + (bias ? bias[i] : 0.f); };
+  // one pass over the row: bias added, kept in shared memory, the squares of the query and of the key columns summed
+  float sq = 0.f, sk = 0.f;
+  for (int i = threadIdx.x; i < n_all; i += blockDim.x) {
+    const float v = row[i] + (bias ? bias[i] : 0.f);
+    vals[i] = v;
+    if (i < nq) sq += v * v;
+    else if (i < nq + nk) sk += v * v;
+  }
   float inv_q = 1.f, inv_k = 1.f;
-  __syncthreads();                          // the table is whole
-  if (q_weight != nullptr) {
-    float sq = 0.f;
-    for (int i = threadIdx.x; i < nq; i += blockDim.x) { const float v = val(i); sq += v * v; }
-    inv_q = 1.0f / sqrtf(block_sum(sq, red) / (float)(H * dim) + eps);
-  }
-  if (k_weight != nullptr && G > 0) {
-    float sk = 0.f;
-    for (int i = threadIdx.x; i < nk; i += blockDim.x) { const float v = val(nq + i); sk += v * v; }
-    inv_k = 1.0f / sqrtf(block_sum(sk, red) / (float)(G * dim) + eps);
-  }
-  // element d of a head that starts at column ``base``, normalised and rotated
+  if (q_weight != nullptr) inv_q = 1.0f / sqrtf(block_sum(sq, red) / (float)(H * dim) + eps);
+  if (k_weight != nullptr && G > 0) inv_k = 1.0f / sqrtf(block_sum(sk, red) / (float)(G * dim) + eps);
+  __syncthreads();                          // the table and the row are whole
+  // element d of a head that starts at column ``base`` (its weights at ``w_base``), normalised and rotated
   auto prepared = [&](int base, int w_base, int d, float inv, const float* w) {
-    auto normed = [&](int e) { const float v = val(base + e); return w ? v * inv * w[w_base + e] : v; };
+    auto normed = [&](int e) { const float v = vals[base + e]; return w ? v * inv * w[w_base + e] : v; };
     const float v = normed(d);
     if (d >= rot) return v;
     const int j = d < half ? d : d - half;
@@ -423,7 +426,7 @@ __global__ void __launch_bounds__(256) qk_prepare_kernel(
     const int g = i / D, d = i - g * D;
     const size_t off = (((size_t)page * G + g) * ps + within) * D + d;
     kc[off] = from_float<T>(prepared(nq + g * D, g * D, d, inv_k, k_weight));
-    vc[off] = from_float<T>(val(nq + nk + i));
+    vc[off] = from_float<T>(vals[nq + nk + i]);
   }
 }
 
@@ -495,8 +498,12 @@ SB_EXPORT int sb_qk_prepare(const float* sums, int stride, const float* bias, co
   if (H <= 0 || G < 0 || D <= 0 || dim <= 0 || dim > D || stride < (H + 2 * G) * D || q_stride < H * D) return SB_ERR_SHAPE;
   if (rot < 0 || (rot & 1) || rot > dim || (rot > 0 && !inv_freq)) return SB_ERR_SHAPE;
   if (G > 0 && (ps <= 0 || bt_width <= 0 || !kc || !vc || !errors)) return SB_ERR_SHAPE;
-  const size_t smem = (size_t)(rot > 0 ? rot : 2) * sizeof(float);
-  if (smem > 40 * 1024) return SB_ERR_LIMIT;
+  const size_t smem = ((size_t)(rot > 0 ? rot : 2) + (size_t)(H + 2 * G) * D) * sizeof(float);
+  if (smem > 200 * 1024) return SB_ERR_LIMIT;
+  if (smem > 48 * 1024) {
+    cudaFuncSetAttribute(qk_prepare_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaFuncSetAttribute(qk_prepare_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  }
   if (dtype == SB_DTYPE_F32)
     qk_prepare_kernel<float><<<n_tokens, 256, smem, stream>>>(sums, stride, bias, positions, token_row, H, G, D, dim, q_weight, k_weight, eps,
                                                             inv_freq, rot, (float*)q_out, q_stride, (float*)kc, (float*)vc, block_table,

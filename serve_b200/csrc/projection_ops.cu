@@ -400,33 +400,40 @@ __global__ void __launch_bounds__(256) qk_prepare_kernel(
   if (q_weight != nullptr) inv_q = 1.0f / sqrtf(block_sum(sq, red) / (float)(H * dim) + eps);
   if (k_weight != nullptr && G > 0) inv_k = 1.0f / sqrtf(block_sum(sk, red) / (float)(G * dim) + eps);
   __syncthreads();                          // the table and the row are whole
-  // element d of a head that starts at column ``base`` (its weights at ``w_base``), normalised and rotated
-  auto prepared = [&](int base, int w_base, int d, float inv, const float* w) {
-    auto normed = [&](int e) { const float v = vals[base + e]; return w ? v * inv * w[w_base + e] : v; };
-    const float v = normed(d);
-    if (d >= rot) return v;
-    const int j = d < half ? d : d - half;
-    const float cs = cs_table[j], sn = cs_table[half + j];
-    const float other = normed(d < half ? d + half : d - half);
-    return d < half ? v * cs - other * sn : v * cs + other * sn;
-  };
-  for (int i = threadIdx.x; i < nq; i += blockDim.x) {
-    const int h = i / D, d = i - h * D;
-    q_out[(size_t)t * q_stride + i] = from_float<T>(prepared(h * D, h * D, d, inv_q, q_weight));
-  }
-  if (G == 0) return;
-  const int blk = pos / ps;
-  const int page = (pos >= 0 && blk < bt_width) ? block_table[(size_t)token_row[t] * bt_width + blk] : -1;
-  if (page < 0 || page >= num_pages) {
-    if (threadIdx.x == 0) atomicAdd(errors, 1);
-    return;
-  }
+  // A warp takes a head at a time, a lane an element; an element below rot / 2 is turned together with its partner rot / 2
+  // further on, so every value is normalised once. Heads 0 .. H-1 are queries, the G after them keys.
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+  const int blk = ps > 0 ? pos / ps : 0;
+  const int page = (G > 0 && pos >= 0 && blk < bt_width) ? block_table[(size_t)token_row[t] * bt_width + blk] : -1;
+  const bool page_ok = page >= 0 && page < num_pages;
+  if (G > 0 && !page_ok && threadIdx.x == 0) atomicAdd(errors, 1);
   const int within = pos - blk * ps;
+  for (int head = warp; head < H + G; head += n_warps) {
+    const bool is_q = head < H;
+    if (!is_q && !page_ok) continue;
+    const float* w = is_q ? q_weight : k_weight;
+    const float inv = is_q ? inv_q : inv_k;
+    const int base = head * D, w_base = is_q ? base : base - nq;
+    T* dst = is_q ? q_out + (size_t)t * q_stride + base : kc + (((size_t)page * G + (head - H)) * ps + within) * D;
+    for (int d = lane; d < D; d += 32) {
+      if (d >= half && d < rot) continue;                    // written by its partner
+      float v = vals[base + d];
+      if (w) v *= inv * w[w_base + d];
+      if (d < half) {
+        float o = vals[base + d + half];
+        if (w) o *= inv * w[w_base + d + half];
+        const float cs = cs_table[d], sn = cs_table[half + d];
+        dst[d] = from_float<T>(v * cs - o * sn);
+        dst[d + half] = from_float<T>(o * cs + v * sn);
+      } else {
+        dst[d] = from_float<T>(v);
+      }
+    }
+  }
+  if (!page_ok) return;
   for (int i = threadIdx.x; i < nk; i += blockDim.x) {
     const int g = i / D, d = i - g * D;
-    const size_t off = (((size_t)page * G + g) * ps + within) * D + d;
-    kc[off] = from_float<T>(prepared(nq + g * D, g * D, d, inv_k, k_weight));
-    vc[off] = from_float<T>(vals[nq + nk + i]);
+    vc[(((size_t)page * G + g) * ps + within) * D + d] = from_float<T>(vals[nq + nk + i]);
   }
 }
 

@@ -533,21 +533,45 @@ __global__ void __launch_bounds__(128) kv_norm_cache_write_kernel(const T* __res
 // the row's state (float [slots, C]: the input of the request's last token so far, zeros at the start). A thread per
 // (token, channel) computes every blend of it. With one token a row (pure_decode) the same thread then stores its
 // input as the new state; otherwise token_shift_state_kernel does, in a launch of its own after every read.
-template <typename T>
+template <typename T, int VEC>
 __global__ void __launch_bounds__(256) token_shift_kernel(const T* __restrict__ x, int x_stride, const float* __restrict__ mu, int n_mix,
                                                           float* __restrict__ state, long long slot_stride, const int* __restrict__ slots,
                                                           const int* __restrict__ cu_q, const int* __restrict__ token_row,
                                                           T* __restrict__ out, long long mix_stride, int out_stride, int C, int pure_decode) {
+  // VEC neighbouring channels a thread (16 bytes of activations at a time when VEC > 1; the launcher checks the alignment)
   const int t = blockIdx.y;
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
   if (c >= C) return;
   const int r = token_row[t];
-  const float cur = to_float(x[(size_t)t * x_stride + c]);
   float* st = state + (size_t)slots[r] * slot_stride + c;
-  const float prev = t > cu_q[r] ? to_float(x[(size_t)(t - 1) * x_stride + c]) : *st;
-  const float d = prev - cur;
-  for (int m = 0; m < n_mix; ++m) out[(size_t)m * mix_stride + (size_t)t * out_stride + c] = from_float<T>(cur + d * mu[(size_t)m * C + c]);
-  if (pure_decode) *st = cur;
+  const bool first = t <= cu_q[r];
+  float cur[VEC], d[VEC];
+  if (VEC > 1) {
+    __align__(16) T a[VEC];
+    __align__(16) T b[VEC];
+    *reinterpret_cast<uint4*>(a) = *reinterpret_cast<const uint4*>(x + (size_t)t * x_stride + c);
+    if (!first) *reinterpret_cast<uint4*>(b) = *reinterpret_cast<const uint4*>(x + (size_t)(t - 1) * x_stride + c);
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) {
+      cur[v] = to_float(a[v]);
+      d[v] = (first ? st[v] : to_float(b[v])) - cur[v];
+    }
+  } else {
+    cur[0] = to_float(x[(size_t)t * x_stride + c]);
+    d[0] = (first ? st[0] : to_float(x[(size_t)(t - 1) * x_stride + c])) - cur[0];
+  }
+  for (int m = 0; m < n_mix; ++m) {
+    __align__(16) T o[VEC];
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) o[v] = from_float<T>(cur[v] + d[v] * mu[(size_t)m * C + c + v]);
+    T* dst = out + (size_t)m * mix_stride + (size_t)t * out_stride + c;
+    if (VEC > 1) *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(o);
+    else dst[0] = o[0];
+  }
+  if (pure_decode) {
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) st[v] = cur[v];
+  }
 }
 
 template <typename T>
@@ -571,16 +595,20 @@ SB_EXPORT int sb_token_shift(const void* x, int x_stride, const float* mu, int n
   if (n_tokens <= 0 || C <= 0) return 0;
   if (n_mix <= 0 || !state || x == out) return SB_ERR_SHAPE;
   if (n_tokens > 65535 || n_rows > 65535 || n_rows <= 0) return SB_ERR_LIMIT;
-  dim3 grid((C + 255) / 256, n_tokens), sgrid(grid.x, n_rows);
+  const int esz = dtype == SB_DTYPE_F32 ? 4 : 2, per = 16 / esz;
+  const bool vec = C % per == 0 && x_stride % per == 0 && out_stride % per == 0 && mix_stride % per == 0 && aligned16(x) && aligned16(out);
+  dim3 sgrid((C + 255) / 256, n_rows), grid(vec ? (C / per + 255) / 256 : (C + 255) / 256, n_tokens);
   if (dtype == SB_DTYPE_F32) {
-    token_shift_kernel<float><<<grid, 256, 0, stream>>>((const float*)x, x_stride, mu, n_mix, state, slot_stride, slots, cu_q, token_row,
-                                                         (float*)out, mix_stride, out_stride, C, pure_decode);
+    auto k = vec ? token_shift_kernel<float, 4> : token_shift_kernel<float, 1>;
+    k<<<grid, 256, 0, stream>>>((const float*)x, x_stride, mu, n_mix, state, slot_stride, slots, cu_q, token_row, (float*)out, mix_stride,
+                                out_stride, C, pure_decode);
     SB_LAUNCH_CHECK();
     if (!pure_decode) token_shift_state_kernel<float><<<sgrid, 256, 0, stream>>>((const float*)x, x_stride, state, slot_stride, slots, cu_q, C);
   } else if (dtype == SB_DTYPE_BF16) {
     typedef __nv_bfloat16 B;
-    token_shift_kernel<B><<<grid, 256, 0, stream>>>((const B*)x, x_stride, mu, n_mix, state, slot_stride, slots, cu_q, token_row, (B*)out,
-                                                     mix_stride, out_stride, C, pure_decode);
+    auto k = vec ? token_shift_kernel<B, 8> : token_shift_kernel<B, 1>;
+    k<<<grid, 256, 0, stream>>>((const B*)x, x_stride, mu, n_mix, state, slot_stride, slots, cu_q, token_row, (B*)out, mix_stride, out_stride,
+                                C, pure_decode);
     SB_LAUNCH_CHECK();
     if (!pure_decode) token_shift_state_kernel<B><<<sgrid, 256, 0, stream>>>((const B*)x, x_stride, state, slot_stride, slots, cu_q, C);
   } else {

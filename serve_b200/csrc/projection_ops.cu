@@ -373,7 +373,7 @@ __global__ void __launch_bounds__(256) add_bias_kernel(float* __restrict__ x, co
 // until the one rounding at the store. The row (with its bias) and the token's cosines and sines are kept in shared
 // memory, so the sums are read from memory once (rows of up to 200 KB).
 template <typename T>
-__global__ void __launch_bounds__(256) qk_prepare_kernel(
+__global__ void __launch_bounds__(512) qk_prepare_kernel(
     const float* __restrict__ sums, int stride, const float* __restrict__ bias, const int* __restrict__ positions,
     const int* __restrict__ token_row, int H, int G, int D, int dim, const float* __restrict__ q_weight, const float* __restrict__ k_weight,
     float eps, const float* __restrict__ inv_freq, int rot, T* __restrict__ q_out, int q_stride, T* __restrict__ kc, T* __restrict__ vc,
@@ -390,6 +390,7 @@ __global__ void __launch_bounds__(256) qk_prepare_kernel(
   for (int j = threadIdx.x; j < half; j += blockDim.x) sincosf((float)pos * inv_freq[j], &cs_table[half + j], &cs_table[j]);
   // one pass over the row: bias added, kept in shared memory, the squares of the query and of the key columns summed
   float sq = 0.f, sk = 0.f;
+#pragma unroll 4      // (the loads of several rounds are in flight together: a decoding step has few blocks and waits on each)
   for (int i = threadIdx.x; i < n_all; i += blockDim.x) {
     const float v = row[i] + (bias ? bias[i] : 0.f);
     vals[i] = v;
@@ -507,16 +508,17 @@ SB_EXPORT int sb_qk_prepare(const float* sums, int stride, const float* bias, co
   if (G > 0 && (ps <= 0 || bt_width <= 0 || !kc || !vc || !errors)) return SB_ERR_SHAPE;
   const size_t smem = ((size_t)(rot > 0 ? rot : 2) + (size_t)(H + 2 * G) * D) * sizeof(float);
   if (smem > 200 * 1024) return SB_ERR_LIMIT;
+  const int threads = (H + 2 * G) * D >= 2048 ? 512 : 256;
   if (smem > 48 * 1024) {
     cudaFuncSetAttribute(qk_prepare_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     cudaFuncSetAttribute(qk_prepare_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   }
   if (dtype == SB_DTYPE_F32)
-    qk_prepare_kernel<float><<<n_tokens, 256, smem, stream>>>(sums, stride, bias, positions, token_row, H, G, D, dim, q_weight, k_weight, eps,
+    qk_prepare_kernel<float><<<n_tokens, threads, smem, stream>>>(sums, stride, bias, positions, token_row, H, G, D, dim, q_weight, k_weight, eps,
                                                             inv_freq, rot, (float*)q_out, q_stride, (float*)kc, (float*)vc, block_table,
                                                             bt_width, ps, num_pages, errors);
   else if (dtype == SB_DTYPE_BF16)
-    qk_prepare_kernel<__nv_bfloat16><<<n_tokens, 256, smem, stream>>>(sums, stride, bias, positions, token_row, H, G, D, dim, q_weight, k_weight,
+    qk_prepare_kernel<__nv_bfloat16><<<n_tokens, threads, smem, stream>>>(sums, stride, bias, positions, token_row, H, G, D, dim, q_weight, k_weight,
                                                                     eps, inv_freq, rot, (__nv_bfloat16*)q_out, q_stride, (__nv_bfloat16*)kc,
                                                                     (__nv_bfloat16*)vc, block_table, bt_width, ps, num_pages, errors);
   else

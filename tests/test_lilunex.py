@@ -711,3 +711,33 @@ def test_trace_run_and_command_line_programs(models, tmp_path):
     new = json.loads([l for l in out.stdout.splitlines() if l.startswith("{")][-1])["generated_tokens"]
     logits = plain_logits(w, CONFIGS["a"], prompt + new)
     assert all(int(logits[len(prompt) - 1 + i].argmax()) == t for i, t in enumerate(new))
+
+
+ONE_KIND = {
+    "recurrent": {"architecture": "Lilunex", "width": 64, "vocab": 90, "norm": {"eps": 1e-5}, "embedding": {"scale": 3.0}, "layers": [
+        {"type": "wkv", "mixer": WKV(2, 16), "mlp": None}, {"type": "delta", "mixer": DELTA(2, 1, 16, 16, 3), "mlp": None}]},
+    "attention": {"architecture": "Lilunex", "width": 64, "vocab": 90, "norm": {"eps": 1e-5}, "embedding": {"scale": 3.0}, "layers": [
+        {"type": "attention", "mixer": ATT(2, 1, 16, 16, 0.25, 300, 0, 1000.0, 16, 1.0), "mlp": {"kind": "dense", "ff": 64}},
+        {"type": "attention", "mixer": ATT(2, 1, 16, 16, 0.25, 5, 1, 1000.0, 16, 1.0, kv_from=0), "mlp": None},
+        {"type": "attention", "mixer": ATT(4, 4, 8, 8, 0.3, 9, 2, 1000.0, 4, 3.0), "mlp": None},
+        {"type": "attention", "mixer": ATT(2, 1, 16, 16, 0.25, 11, 20, 1000.0, 16, 1.0, kv_from=0), "mlp": MOE(2, 0, 2, 16)}]},
+}
+
+
+@pytest.mark.parametrize("backend", BACKENDS)
+@pytest.mark.parametrize("kind", sorted(ONE_KIND))
+def test_models_of_one_kind_of_layer(backend, kind, tmp_path):
+    """No cached keys at all (no page group, only states), and nothing but attention (no state; two layers read the
+    first one's keys through windows of their own, one of them with more kept tokens than its window is long)."""
+    cfg = ONE_KIND[kind]
+    w = make_weights(cfg, 7)
+    folder = write_model(str(tmp_path / kind), cfg, w, getattr(torch, backend[1]))
+    reqs = {f"r{i}": helpers.random_tokens(cfg["vocab"], n, seed=i) for i, n in enumerate([70, 3, 41])}
+    plain = {rid: plain_logits(w, cfg, t) for rid, t in reqs.items()}
+    eng = make_engine(folder, backend, 8, num_pages=24, max_slots=2)
+    assert len(eng.cache.groups) == (0 if kind == "recurrent" else 2)
+    with torch.inference_mode():
+        got = helpers.replay(eng, helpers.trace_mixed(reqs, live=2, seed=3))
+    eng.kernels.check_errors()
+    compare_rows(got, plain, backend)
+    assert eng.cache.live == 0

@@ -17,7 +17,7 @@ from .base import ConfigError, ModelConfig
 
 _MIXER_KEYS = {
     "wkv": ("heads", "dim"),
-    "attention": ("heads", "kv_heads", "dim", "vdim", "scale", "mask", "rot"),
+    "attention": ("heads", "kv_heads", "dim", "vdim", "scale"),
     "delta": ("heads", "kv_heads", "dim", "vdim", "conv"),
 }
 
@@ -82,18 +82,20 @@ class LilunexConfig(ModelConfig):
                 _positive(m, ("heads", "kv_heads", "dim", "vdim"), where + ".mixer")
                 if m["heads"] % m["kv_heads"]:
                     raise ConfigError(f"{where}.mixer: heads must be a multiple of kv_heads")
-                _need(m["mask"], ("size",), where + ".mixer.mask")
-                _positive(m["mask"], ("size",), where + ".mixer.mask")
-                keep = m["mask"].get("keep_first") or 0
-                if not isinstance(keep, int) or keep < 0:
-                    raise ConfigError(f"{where}.mixer.mask.keep_first must be a count, got {keep!r}")
-                _need(m["rot"], ("base", "dims"), where + ".mixer.rot")
-                if not isinstance(m["rot"]["dims"], int) or m["rot"]["dims"] < 0 or m["rot"]["dims"] % 2 or m["rot"]["dims"] > m["dim"]:
-                    raise ConfigError(f"{where}.mixer.rot.dims must be even and at most dim")
-                if m["rot"].get("scaling") is not None:
-                    _need(m["rot"]["scaling"], ("factor",), where + ".mixer.rot.scaling")
-                    if not float(m["rot"]["scaling"]["factor"]) > 0:
-                        raise ConfigError(f"{where}.mixer.rot.scaling.factor must be positive")
+                if m.get("mask") is not None:       # without a mask every earlier position is seen
+                    _need(m["mask"], ("size",), where + ".mixer.mask")
+                    _positive(m["mask"], ("size",), where + ".mixer.mask")
+                    keep = m["mask"].get("keep_first") or 0
+                    if not isinstance(keep, int) or keep < 0:
+                        raise ConfigError(f"{where}.mixer.mask.keep_first must be a count, got {keep!r}")
+                if m.get("rot") is not None:        # without a rotation queries and keys carry no position
+                    _need(m["rot"], ("base", "dims"), where + ".mixer.rot")
+                    if not isinstance(m["rot"]["dims"], int) or m["rot"]["dims"] < 0 or m["rot"]["dims"] % 2 or m["rot"]["dims"] > m["dim"]:
+                        raise ConfigError(f"{where}.mixer.rot.dims must be even and at most dim")
+                    if m["rot"].get("scaling") is not None:
+                        _need(m["rot"]["scaling"], ("factor",), where + ".mixer.rot.scaling")
+                        if not float(m["rot"]["scaling"]["factor"]) > 0:
+                            raise ConfigError(f"{where}.mixer.rot.scaling.factor must be positive")
                 src = m.get("kv_from")
                 if src is not None:
                     if not isinstance(src, int) or not (0 <= src < i):

@@ -29,11 +29,12 @@ def _mixer_spec(kind: str, m: dict, width: int, eps: float, prefix: str) -> Part
         return PartSpec("gated_delta", {
             "hidden": width, "heads": m["heads"], "kv_heads": m["kv_heads"], "dim": m["dim"], "vdim": m["vdim"], "taps": m["conv"],
             "eps": eps, "decay_per": "head", "low_rank": False, "gate": "silu", "names": {"rate": "a", "gate": "g"}}, prefix)
-    rot = m["rot"]
+    rot = m.get("rot") or {"dims": 0, "base": 10000.0}
+    mask = m.get("mask") or {}
     factor = float(rot["scaling"]["factor"]) if rot.get("scaling") is not None else 1.0
     return PartSpec("rotary_sink_attention", {
         "hidden": width, "heads": m["heads"], "kv_heads": m["kv_heads"], "dim": m["dim"], "vdim": m["vdim"], "scale": m["scale"],
-        "bias": True, "qk_norm_eps": eps, "sink": True, "window": m["mask"]["size"], "keep_first": m["mask"].get("keep_first") or 0,
+        "bias": True, "qk_norm_eps": eps, "sink": True, "window": mask.get("size"), "keep_first": mask.get("keep_first") or 0,
         "own_kv": m.get("kv_from") is None,
         "position": PartSpec("rotary", {"rotary_dim": rot["dims"], "theta": rot["base"], "pairing": "half",
                                         "scaling": {"kind": "linear", "factor": factor} if factor != 1.0 else None})}, prefix)

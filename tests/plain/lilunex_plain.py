@@ -78,8 +78,13 @@ def wkv_mixer(h, w, p, m, eps):
 
 
 def _rot_factor(m) -> float:
-    scaling = m["rot"].get("scaling")
+    scaling = (m.get("rot") or {}).get("scaling")
     return float(scaling["factor"]) if scaling else 1.0
+
+
+def _rotated(x, m):
+    rot = m.get("rot")
+    return rotate_half_layout(x, rot["base"], rot["dims"], _rot_factor(m)) if rot else x
 
 
 def attention_keys_values(h, w, p, m, eps):
@@ -89,7 +94,7 @@ def attention_keys_values(h, w, p, m, eps):
     k = h @ w[p + "k"].T + w[p + "k.b"]
     v = h @ w[p + "v"].T + w[p + "v.b"]
     k = unit_rms(k, eps) * w[p + "k.norm"]
-    k = rotate_half_layout(k.view(t, g, dim), m["rot"]["base"], m["rot"]["dims"], _rot_factor(m))
+    k = _rotated(k.view(t, g, dim), m)
     return k, v.view(t, g, vdim)
 
 
@@ -99,8 +104,9 @@ def attention_mixer(h, w, p, m, eps, k, v):
     t = h.shape[0]
     q = h @ w[p + "q"].T + w[p + "q.b"]
     q = unit_rms(q, eps) * w[p + "q.norm"]
-    q = rotate_half_layout(q.view(t, heads, dim), m["rot"]["base"], m["rot"]["dims"], _rot_factor(m))
-    size, keep = m["mask"]["size"], m["mask"].get("keep_first") or 0
+    q = _rotated(q.view(t, heads, dim), m)
+    mask = m.get("mask")
+    size, keep = (mask["size"], mask.get("keep_first") or 0) if mask else (t + 1, 0)
     allowed = torch.tensor([[visible(i, j, size, keep) for j in range(t)] for i in range(t)])
     out = torch.zeros(t, heads, vdim, dtype=h.dtype)
     for n in range(heads):

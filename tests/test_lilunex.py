@@ -242,7 +242,8 @@ WKVS = [WKV(2, 16), WKV(5, 12), WKV(1, 32), WKV(3, 64)]
 DELTAS = [DELTA(4, 2, 16, 24, 4), DELTA(3, 3, 12, 20, 3), DELTA(6, 2, 8, 8, 2), DELTA(2, 1, 64, 32, 4)]
 ATTS = [ATT(4, 2, 24, 16, 0.2, 20, 3, 10000.0, 16, 2.0), ATT(6, 1, 20, 12, 0.3, 7, None, 3000.0, 10, None),
         ATT(6, 3, 8, 8, 0.35, 64, 17, 100.0, 8, 8.0), ATT(2, 2, 16, 40, 0.25, 9, 9, 500.0, 0, None),
-        ATT(3, 1, 32, 32, 0.18, 1, 2, 20000.0, 32, 0.5)]
+        ATT(3, 1, 32, 32, 0.18, 1, 2, 7000.0, 32, 0.5),
+        {"heads": 4, "kv_heads": 2, "dim": 16, "vdim": 16, "scale": 0.3}]     # no mask and no rotation in the file
 
 
 @pytest.mark.parametrize("backend", BACKENDS)
@@ -264,8 +265,9 @@ def test_gated_delta_alone(backend, cuts, which):
 @pytest.mark.parametrize("which", range(len(ATTS)))
 def test_attention_alone(backend, cuts, which):
     """Also: no rotation at all, a window of one key (the query's own) with two kept tokens, value heads wider than the
-    keys', a window as long as the kept tokens."""
-    _mixer_alone(backend, _single("attention", ATTS[which], width=(64, 100, 48, 40, 72)[which]), cuts)
+    keys', a window as long as the kept tokens, a mixer whose file names neither a mask nor a rotation (every earlier
+    position is seen, no position signal)."""
+    _mixer_alone(backend, _single("attention", ATTS[which], width=(64, 100, 48, 40, 72, 56)[which]), cuts)
 
 
 def test_the_first_tokens_of_a_sequence_start_from_zeros():

@@ -182,11 +182,13 @@ struct RecArgs {
   float *qf, *kf, *af, *vf, *sc, *dec;
 };
 
-// grid (tokens, max(H, Hqk)); 128 threads.
+// A warp per (token, head) of max(H, Hqk) heads, four warps a block: a head has a few dozen to a few hundred elements.
 template <typename T, int MODE>
 __global__ void __launch_bounds__(REC_THREADS) recurrence_prep_kernel(RecArgs a) {
-  __shared__ float red[32];
-  const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+  const int heads = a.H > a.Hqk ? a.H : a.Hqk;
+  const long long wid = (long long)blockIdx.x * (REC_THREADS / 32) + (threadIdx.x >> 5);
+  if (wid >= (long long)a.n_tokens * heads) return;      // (a whole warp leaves together; nothing below waits for the block)
+  const int t = (int)(wid / heads), h = (int)(wid - (long long)t * heads), tid = threadIdx.x & 31;
   const int dk = a.dk, dkp = a.dkp, dv = a.dv, dvp = a.dvp;
   if (h < a.Hqk) {
     const T* qr = (const T*)a.q + (size_t)t * a.q_stride + (size_t)h * dk;
@@ -196,17 +198,17 @@ __global__ void __launch_bounds__(REC_THREADS) recurrence_prep_kernel(RecArgs a)
     float fq = 1.f, fk = 1.f;
     if (MODE == MODE_DELTA) {
       float sq = 0.f, sk = 0.f;
-      for (int i = tid; i < dk; i += REC_THREADS) {
+      for (int i = tid; i < dk; i += 32) {
         const float x = to_float(qr[i]), y = to_float(kr[i]);
         sq += x * x;
         sk += y * y;
       }
-      sq = block_sum(sq, red);
-      sk = block_sum(sk, red);
+      sq = warp_sum(sq);
+      sk = warp_sum(sk);
       fq = a.q_scale / sqrtf(sq + 1e-6f);
       fk = 1.f / sqrtf(sk + 1e-6f);
     }
-    for (int i = tid; i < dkp; i += REC_THREADS) {
+    for (int i = tid; i < dkp; i += 32) {
       float x = 0.f, y = 0.f;
       if (i < dk) {
         x = to_float(qr[i]);
@@ -222,7 +224,7 @@ __global__ void __launch_bounds__(REC_THREADS) recurrence_prep_kernel(RecArgs a)
   if (h < a.H) {
     const T* vr = (const T*)a.v + (size_t)t * a.v_stride + (size_t)h * dv;
     float* vo = a.vf + ((size_t)t * a.H + h) * dvp;
-    for (int j = tid; j < dvp; j += REC_THREADS) {
+    for (int j = tid; j < dvp; j += 32) {
       float x = j < dv ? to_float(vr[j]) : 0.f;
       if (MODE == MODE_DECAY) x = silu_f(x);
       vo[j] = x;
@@ -232,10 +234,10 @@ __global__ void __launch_bounds__(REC_THREADS) recurrence_prep_kernel(RecArgs a)
       float* ao = a.af + ((size_t)t * a.H + h) * dkp;
       if (a.rate_per_head) {                   // one decay for all rows of the head's state
         const float g = expf(neg_a * softplus_f(load_w(a.rate, a.rate_dtype, (size_t)t * a.rate_stride + h) + load_w(a.dt_bias, a.par_dtype, h)));
-        for (int i = tid; i < dkp; i += REC_THREADS) ao[i] = i < dk ? g : 1.f;
+        for (int i = tid; i < dkp; i += 32) ao[i] = i < dk ? g : 1.f;
       } else {
         const size_t r0 = (size_t)t * a.rate_stride + (size_t)h * dk;
-        for (int i = tid; i < dkp; i += REC_THREADS)
+        for (int i = tid; i < dkp; i += 32)
           ao[i] = i < dk ? expf(neg_a * softplus_f(load_w(a.rate, a.rate_dtype, r0 + i) + load_w(a.dt_bias, a.par_dtype, (size_t)h * dk + i))) : 1.f;
       }
     }
@@ -246,11 +248,11 @@ __global__ void __launch_bounds__(REC_THREADS) recurrence_prep_kernel(RecArgs a)
       const T* qr = (const T*)a.q + (size_t)t * a.q_stride + (size_t)h * dk;
       const T* kr = (const T*)a.k + (size_t)t * a.k_stride + (size_t)h * dk;
       float* ao = a.af + ((size_t)t * a.H + h) * dkp;
-      for (int i = tid; i < dkp; i += REC_THREADS) {
+      for (int i = tid; i < dkp; i += 32) {
         ao[i] = i < dk ? expf(-expf(load_w(a.rate, a.rate_dtype, r0 + i) + load_w(a.dt_bias, a.par_dtype, (size_t)h * dk + i))) : 1.f;
         if (i < dk) bonus_dot += to_float(qr[i]) * a.bonus[(size_t)h * dk + i] * to_float(kr[i]);
       }
-      bonus_dot = block_sum(bonus_dot, red);
+      bonus_dot = warp_sum(bonus_dot);
     }
     if (tid == 0) {
       float sc = 1.f, dec = 1.f;
@@ -428,7 +430,10 @@ int launch_recurrence(RecArgs a, float* work, int n_rows, cudaStream_t stream) {
   a.sc = a.vf + T_ * a.H * a.dvp;
   a.dec = a.sc + T_ * a.H;
   if (a.n_tokens > 0x7fffffff / 1 || a.H > 65535 || a.Hqk > 65535) return SB_ERR_LIMIT;
-  recurrence_prep_kernel<T, MODE><<<dim3(a.n_tokens, a.H > a.Hqk ? a.H : a.Hqk), REC_THREADS, 0, stream>>>(a);
+  const long long prep_warps = (long long)a.n_tokens * (a.H > a.Hqk ? a.H : a.Hqk);
+  const long long prep_blocks = (prep_warps + REC_THREADS / 32 - 1) / (REC_THREADS / 32);
+  if (prep_blocks > 0x7fffffffLL) return SB_ERR_LIMIT;
+  recurrence_prep_kernel<T, MODE><<<(unsigned)prep_blocks, REC_THREADS, 0, stream>>>(a);
   SB_LAUNCH_CHECK();
   const int per_tok = ((MODE == MODE_DELTA || MODE == MODE_WKV) ? 3 : 2) * a.dkp + VC;
   const size_t smem = (size_t)2 * (REC_TS * per_tok + 2 * REC_TS) * sizeof(float);
@@ -486,6 +491,67 @@ __global__ void __launch_bounds__(128) gated_norm_kernel(const void* __restrict_
     if (weight) v *= load_w(weight, w_dtype, c % w_size);
     if (gr && !gate_first) v *= gate_of(c);
     out[(size_t)t * out_stride + c] = from_float<T>(v * scale);
+  }
+}
+
+// The same for the shape the recurrent read-outs have: float y, groups of a multiple of 4 up to 512 values that are all
+// normalised, the gate (one value an element, applied last) and the weight optional. A warp per (token, group); a lane
+// loads four neighbours at a time and keeps its share of the group in registers, so y and the gate are read once.
+template <typename T> struct Vec4 { };
+template <> struct Vec4<float> {
+  static __device__ __forceinline__ void load(const float* p, float (&o)[4]) { const float4 x = *(const float4*)p; o[0] = x.x; o[1] = x.y; o[2] = x.z; o[3] = x.w; }
+  static __device__ __forceinline__ void store(float* p, const float (&o)[4]) { *(float4*)p = make_float4(o[0], o[1], o[2], o[3]); }
+};
+template <> struct Vec4<__nv_bfloat16> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&o)[4]) {
+    const uint2 x = *(const uint2*)p;
+    const __nv_bfloat162 a = *(const __nv_bfloat162*)&x.x, b = *(const __nv_bfloat162*)&x.y;
+    o[0] = __low2float(a); o[1] = __high2float(a); o[2] = __low2float(b); o[3] = __high2float(b);
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&o)[4]) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(o[0], o[1]), b = __floats2bfloat162_rn(o[2], o[3]);
+    uint2 x;
+    x.x = *(const unsigned*)&a; x.y = *(const unsigned*)&b;
+    *(uint2*)p = x;
+  }
+};
+
+template <typename T, typename W>
+__global__ void __launch_bounds__(128) gated_norm_vec_kernel(const float* __restrict__ y, int y_stride, const T* __restrict__ gate, int gate_stride,
+                                                             int gate_act, const W* __restrict__ weight, int w_size, T* __restrict__ out,
+                                                             int out_stride, int n_tokens, int gs, int groups, float eps, float scale) {
+  const int lane = threadIdx.x & 31;
+  const long long wid = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (wid >= (long long)n_tokens * groups) return;
+  const int t = (int)(wid / groups), g = (int)(wid - (long long)t * groups), c0 = g * gs;
+  const float* yr = y + (size_t)t * y_stride + c0;
+  float v[4][4];
+  float ss = 0.f;
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const int c = (r * 32 + lane) * 4;
+    if (c < gs) {
+      Vec4<float>::load(yr + c, v[r]);
+      ss += v[r][0] * v[r][0] + v[r][1] * v[r][1] + v[r][2] * v[r][2] + v[r][3] * v[r][3];
+    }
+  }
+  ss = warp_sum(ss);
+  const float inv = scale / sqrtf(ss / (float)gs + eps);
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const int c = (r * 32 + lane) * 4;
+    if (c < gs) {
+      float w[4] = {1.f, 1.f, 1.f, 1.f}, z[4];
+      if (weight) Vec4<W>::load(weight + (c0 + c) % w_size, w);
+      if (gate) {
+        Vec4<T>::load(gate + (size_t)t * gate_stride + c0 + c, z);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) w[i] *= gate_act == 1 ? silu_f(z[i]) : sigmoid_f(z[i]);
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) z[i] = v[r][i] * inv * w[i];
+      Vec4<T>::store(out + (size_t)t * out_stride + c0 + c, z);
+    }
   }
 }
 
@@ -714,6 +780,29 @@ SB_EXPORT int sb_gated_norm(const void* y, int y_dtype, int y_stride, const void
   if (groups <= 0) groups = gate ? gate_cols : 1;
   if (C % groups || (gate && (gate_cols <= 0 || C % gate_cols)) || (weight && (w_size <= 0 || C % w_size))) return SB_ERR_SHAPE;
   const long long warps = (long long)n_tokens * groups;
+  {   // the recurrent read-outs' shape on the kernel that moves 16 bytes a lane
+    const int gs = C / groups, esz = dtype == SB_DTYPE_F32 ? 4 : 2, wsz = w_dtype == SB_DTYPE_F32 ? 4 : 2;
+    const bool fits = normalise && y_dtype == SB_DTYPE_F32 && gs <= 512 && gs % 4 == 0 && y_stride % 4 == 0 && out_stride % 4 == 0 &&
+                      aligned16(y) && (reinterpret_cast<uintptr_t>(out) % (4 * esz)) == 0 &&
+                      (!gate || (!gate_first && gate_cols == C && gate_stride % 4 == 0 && (reinterpret_cast<uintptr_t>(gate) % (4 * esz)) == 0)) &&
+                      (!weight || (w_size % 4 == 0 && (reinterpret_cast<uintptr_t>(weight) % (4 * wsz)) == 0 &&
+                                   (w_dtype == SB_DTYPE_F32 || w_dtype == SB_DTYPE_BF16))) &&
+                      (dtype == SB_DTYPE_F32 || dtype == SB_DTYPE_BF16) && (warps + 3) / 4 <= 0x7fffffffLL;
+    if (fits) {
+      const unsigned nb = (unsigned)((warps + 3) / 4);
+#define SB_GNV(T, W)                                                                                                            \
+  gated_norm_vec_kernel<T, W><<<nb, 128, 0, stream>>>((const float*)y, y_stride, (const T*)gate, gate_stride, gate_act, (const W*)weight, \
+                                                      weight ? w_size : 4, (T*)out, out_stride, n_tokens, gs, groups, eps, scale)
+      if (dtype == SB_DTYPE_F32) {
+        if (w_dtype == SB_DTYPE_F32) SB_GNV(float, float); else SB_GNV(float, __nv_bfloat16);
+      } else {
+        if (w_dtype == SB_DTYPE_F32) SB_GNV(__nv_bfloat16, float); else SB_GNV(__nv_bfloat16, __nv_bfloat16);
+      }
+#undef SB_GNV
+      SB_LAUNCH_CHECK();
+      return 0;
+    }
+  }
   const bool wide = C / groups > 512;                     // a block per group
   const long long blocks = wide ? warps : (warps + 3) / 4;
   if (blocks > 0x7fffffffLL) return SB_ERR_LIMIT;

@@ -516,41 +516,46 @@ template <> struct Vec4<__nv_bfloat16> {
   }
 };
 
+// LPG lanes a group (a power of two, at least gs / 16), so a warp takes 32 / LPG groups at once when they are short.
 template <typename T, typename W>
 __global__ void __launch_bounds__(128) gated_norm_vec_kernel(const float* __restrict__ y, int y_stride, const T* __restrict__ gate, int gate_stride,
                                                              int gate_act, const W* __restrict__ weight, int w_size, T* __restrict__ out,
-                                                             int out_stride, int n_tokens, int gs, int groups, float eps, float scale) {
-  const int lane = threadIdx.x & 31;
-  const long long wid = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
-  if (wid >= (long long)n_tokens * groups) return;
-  const int t = (int)(wid / groups), g = (int)(wid - (long long)t * groups), c0 = g * gs;
+                                                             int out_stride, int n_groups, int gs, int groups, int lpg, float eps, float scale) {
+  const int lane = threadIdx.x & 31, sub = lane & (lpg - 1);
+  const int gid = (blockIdx.x * 4 + (threadIdx.x >> 5)) * (32 / lpg) + lane / lpg;      // (token, group), groups fastest
+  const bool live = gid < n_groups;                                   // (idle lanes still take part in the shuffles)
+  const int t = live ? gid / groups : 0, c0 = live ? (gid - t * groups) * gs : 0;
   const float* yr = y + (size_t)t * y_stride + c0;
   float v[4][4];
   float ss = 0.f;
 #pragma unroll
   for (int r = 0; r < 4; ++r) {
-    const int c = (r * 32 + lane) * 4;
-    if (c < gs) {
+    const int c = (r * lpg + sub) * 4;
+    if (live && c < gs) {
       Vec4<float>::load(yr + c, v[r]);
       ss += v[r][0] * v[r][0] + v[r][1] * v[r][1] + v[r][2] * v[r][2] + v[r][3] * v[r][3];
     }
   }
-  ss = warp_sum(ss);
+  for (int o = lpg >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  if (!live) return;
   const float inv = scale / sqrtf(ss / (float)gs + eps);
+  const int w0 = weight ? c0 % w_size : 0;                            // (the weight's period is a multiple of the group)
+  const T* gr = gate ? gate + (size_t)t * gate_stride + c0 : nullptr;
+  T* orow = out + (size_t)t * out_stride + c0;
 #pragma unroll
   for (int r = 0; r < 4; ++r) {
-    const int c = (r * 32 + lane) * 4;
+    const int c = (r * lpg + sub) * 4;
     if (c < gs) {
       float w[4] = {1.f, 1.f, 1.f, 1.f}, z[4];
-      if (weight) Vec4<W>::load(weight + (c0 + c) % w_size, w);
-      if (gate) {
-        Vec4<T>::load(gate + (size_t)t * gate_stride + c0 + c, z);
+      if (weight) Vec4<W>::load(weight + w0 + c, w);
+      if (gr) {
+        Vec4<T>::load(gr + c, z);
 #pragma unroll
         for (int i = 0; i < 4; ++i) w[i] *= gate_act == 1 ? silu_f(z[i]) : sigmoid_f(z[i]);
       }
 #pragma unroll
       for (int i = 0; i < 4; ++i) z[i] = v[r][i] * inv * w[i];
-      Vec4<T>::store(out + (size_t)t * out_stride + c0 + c, z);
+      Vec4<T>::store(orow + c, z);
     }
   }
 }
@@ -785,14 +790,17 @@ SB_EXPORT int sb_gated_norm(const void* y, int y_dtype, int y_stride, const void
     const bool fits = normalise && y_dtype == SB_DTYPE_F32 && gs <= 512 && gs % 4 == 0 && y_stride % 4 == 0 && out_stride % 4 == 0 &&
                       aligned16(y) && (reinterpret_cast<uintptr_t>(out) % (4 * esz)) == 0 &&
                       (!gate || (!gate_first && gate_cols == C && gate_stride % 4 == 0 && (reinterpret_cast<uintptr_t>(gate) % (4 * esz)) == 0)) &&
-                      (!weight || (w_size % 4 == 0 && (reinterpret_cast<uintptr_t>(weight) % (4 * wsz)) == 0 &&
+                      (!weight || (w_size % gs == 0 && (reinterpret_cast<uintptr_t>(weight) % (4 * wsz)) == 0 &&
                                    (w_dtype == SB_DTYPE_F32 || w_dtype == SB_DTYPE_BF16))) &&
-                      (dtype == SB_DTYPE_F32 || dtype == SB_DTYPE_BF16) && (warps + 3) / 4 <= 0x7fffffffLL;
+                      (dtype == SB_DTYPE_F32 || dtype == SB_DTYPE_BF16) && warps <= 0x7fff0000LL;
     if (fits) {
-      const unsigned nb = (unsigned)((warps + 3) / 4);
+      int lpg = 1;
+      while (lpg * 16 < gs) lpg <<= 1;                                // four rounds of four values a lane cover the group
+      const int per_block = 4 * (32 / lpg);
+      const unsigned nb = (unsigned)((warps + per_block - 1) / per_block);
 #define SB_GNV(T, W)                                                                                                            \
   gated_norm_vec_kernel<T, W><<<nb, 128, 0, stream>>>((const float*)y, y_stride, (const T*)gate, gate_stride, gate_act, (const W*)weight, \
-                                                      weight ? w_size : 4, (T*)out, out_stride, n_tokens, gs, groups, eps, scale)
+                                                      weight ? w_size : gs, (T*)out, out_stride, (int)warps, gs, groups, lpg, eps, scale)
       if (dtype == SB_DTYPE_F32) {
         if (w_dtype == SB_DTYPE_F32) SB_GNV(float, float); else SB_GNV(float, __nv_bfloat16);
       } else {

@@ -6,8 +6,13 @@
 //                             with the logarithm of the position; keys and values into their cache pages
 //   sb_latent_prepare         latent attention: the latent vector normalised, the shared key part and every head's
 //                             rotated query part turned by position; one cache row per token
-//   sb_gated_activation       act(gate, up) of a fused gate/up product: silu(g) * u, or the clamped form
-//                             g <- min(g, limit), u <- clamp(u, -limit, limit), g * sigmoid(alpha g) * (u + 1)
+//   sb_gated_activation       act(gate, up) of a fused gate/up product: silu(g) * u, the clamped form
+//                             g <- min(g, limit), u <- clamp(u, -limit, limit), g * sigmoid(alpha g) * (u + 1), or
+//                             gelu(g) * u with the tanh form of gelu
+//   sb_embedding_pair         x = table[token] * scale + pair_table[row], the row a hash of the token and the one before
+//                             it; a request's last token is kept per state slot for its next portion
+//   sb_bias_round             float sums + bias, rounded once to the activations' type
+//   sb_softcap                l <- c * tanh(l / c) on float logits
 //
 // All arithmetic is float: sums of squares, means, the logarithm, angles (float(position) * frequency, full-precision
 // sincosf) and the activation; T is the storage type of activations and cache pages. Reductions run in a fixed order
@@ -159,13 +164,14 @@ __global__ void __launch_bounds__(256) normed_qk_cache_write_kernel(
 // head columns [q_off, D) of q_lat (rows q_stride apart, heads D apart): the rotated query part, then zeros (columns
 // [0, q_off) are made elsewhere: the product of the plain query part with the keys' read-out matrix when q_off = rank,
 // the plain query part itself when q_off = dim).
-// Rotation: pairs (2 i, 2 i + 1), i < rot_dims / 2, angle = float(position) * inv_freq[i]; the rest passes unchanged.
+// Rotation: pairs (2 i, 2 i + 1), or with half_pairs (i, i + rot_dims / 2), i < rot_dims / 2, angle = float(position) *
+// inv_freq[i]; the rest passes unchanged.
 template <typename T>
 __global__ void __launch_bounds__(128) latent_prepare_kernel(
     const T* __restrict__ proj, int stride, int n_q, const int* __restrict__ positions, const int* __restrict__ token_row,
     const float* __restrict__ c_weight, float eps, const float* __restrict__ inv_freq, int rot_dims, int H, int dim, int rd, int rank,
     int D, T* __restrict__ q_lat, int q_stride, int q_off, T* __restrict__ row_out, int row_stride, T* __restrict__ kc,
-    const int* __restrict__ block_table, int bt_width, int ps, int num_pages, int write_cache, int* __restrict__ errors) {
+    const int* __restrict__ block_table, int bt_width, int ps, int num_pages, int write_cache, int* __restrict__ errors, int half_pairs) {
   __shared__ float red[32];
   extern __shared__ float cs[];            // [rot_dims / 2][2]: cosine and sine of the token's angles
   const int t = blockIdx.x;
@@ -185,6 +191,11 @@ __global__ void __launch_bounds__(128) latent_prepare_kernel(
   // element j of a rotated part whose plain values start at src
   auto rotated = [&](const T* src, int j) -> float {
     if (j >= rot_dims) return to_float(src[j]);
+    if (half_pairs) {
+      const int i = j < half ? j : j - half;
+      const float u = to_float(src[i]), v = to_float(src[i + half]);
+      return j < half ? u * cs[2 * i] - v * cs[2 * i + 1] : v * cs[2 * i] + u * cs[2 * i + 1];
+    }
     const int i = j >> 1;
     const float u = to_float(src[2 * i]), v = to_float(src[2 * i + 1]);
     return (j & 1) ? v * cs[2 * i] + u * cs[2 * i + 1] : u * cs[2 * i] - v * cs[2 * i + 1];
@@ -219,7 +230,9 @@ __global__ void __launch_bounds__(128) latent_prepare_kernel(
 }
 
 // ------------------------------------------------------------------------------------------------ gated activation
-// gate_up [T, 2 I] (gate columns, then up columns) -> out [T, I]. kind 0: silu(g) * u; 1: the clamped form.
+__device__ __forceinline__ float gelu_tanh_f(float z) { return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z))); }
+
+// gate_up [T, 2 I] (gate columns, then up columns) -> out [T, I]. kind 0: silu(g) * u; 1: the clamped form; 2: gelu(g) * u.
 template <typename T>
 __global__ void gated_activation_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, size_t total, int kind, float limit,
                                         float alpha) {
@@ -233,6 +246,8 @@ __global__ void gated_activation_kernel(const T* __restrict__ gate_up, T* __rest
       g = fminf(g, limit);
       u = fminf(fmaxf(u, -limit), limit);
       y = g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
+    } else if (kind == 2) {
+      y = gelu_tanh_f(g) * u;
     } else {
       y = g / (1.0f + expf(-g)) * u;
     }
@@ -261,6 +276,9 @@ __global__ void gated_activation_bf16_vec_kernel(const __nv_bfloat16* __restrict
         u.x = fminf(fmaxf(u.x, -limit), limit); u.y = fminf(fmaxf(u.y, -limit), limit);
         y0 = g.x / (1.0f + expf(-alpha * g.x)) * (u.x + 1.0f);
         y1 = g.y / (1.0f + expf(-alpha * g.y)) * (u.y + 1.0f);
+      } else if (kind == 2) {
+        y0 = gelu_tanh_f(g.x) * u.x;
+        y1 = gelu_tanh_f(g.y) * u.y;
       } else {
         y0 = g.x / (1.0f + expf(-g.x)) * u.x;
         y1 = g.y / (1.0f + expf(-g.y)) * u.y;
@@ -371,13 +389,14 @@ __global__ void __launch_bounds__(256) add_bias_kernel(float* __restrict__ x, co
 // like the padded projection; rotate the first ``rot`` elements of every query and key head, element i with i + rot / 2,
 // by the angle position * inv_freq[i]; queries to q_out [T, H * D], keys and values to their page. Everything is float
 // until the one rounding at the store. The row (with its bias) and the token's cosines and sines are kept in shared
-// memory, so the sums are read from memory once (rows of up to 200 KB).
+// memory, so the sums are read from memory once (rows of up to 200 KB). With head_norm every query and key head is
+// instead divided, after its rotation, by its own root mean square over its dim true elements, without a weight.
 template <typename T>
 __global__ void __launch_bounds__(512) qk_prepare_kernel(
     const float* __restrict__ sums, int stride, const float* __restrict__ bias, const int* __restrict__ positions,
     const int* __restrict__ token_row, int H, int G, int D, int dim, const float* __restrict__ q_weight, const float* __restrict__ k_weight,
     float eps, const float* __restrict__ inv_freq, int rot, T* __restrict__ q_out, int q_stride, T* __restrict__ kc, T* __restrict__ vc,
-    const int* __restrict__ block_table, int bt_width, int ps, int num_pages, int* __restrict__ errors) {
+    const int* __restrict__ block_table, int bt_width, int ps, int num_pages, int* __restrict__ errors, int head_norm) {
   __shared__ float red[32];
   extern __shared__ float dyn[];            // [half] cosines, [half] sines of this token's angles, then the token's row with its bias
   const int t = blockIdx.x;
@@ -416,6 +435,29 @@ __global__ void __launch_bounds__(512) qk_prepare_kernel(
     const float inv = is_q ? inv_q : inv_k;
     const int base = head * D, w_base = is_q ? base : base - nq;
     T* dst = is_q ? q_out + (size_t)t * q_stride + base : kc + (((size_t)page * G + (head - H)) * ps + within) * D;
+    if (head_norm) {
+      // the head is turned in place in shared memory (a lane turns an element together with its partner), its squares are
+      // summed over the warp, and the quotient is stored
+      float ss = 0.f;
+      for (int d = lane; d < D; d += 32) {
+        if (d >= half && d < rot) continue;
+        float v = vals[base + d];
+        if (d < half) {
+          const float o = vals[base + d + half], cs = cs_table[d], sn = cs_table[half + d];
+          const float a = v * cs - o * sn, b = o * cs + v * sn;
+          vals[base + d] = a;
+          vals[base + d + half] = b;
+          ss += a * a + b * b;
+        } else {
+          ss += v * v;                                        // (zero beyond the head's true size)
+        }
+      }
+      ss = warp_sum(ss);
+      __syncwarp();
+      const float inv_h = 1.0f / sqrtf(ss / (float)dim + eps);
+      for (int d = lane; d < D; d += 32) dst[d] = from_float<T>(vals[base + d] * inv_h);
+      continue;
+    }
     for (int d = lane; d < D; d += 32) {
       if (d >= half && d < rot) continue;                    // written by its partner
       float v = vals[base + d];
@@ -501,7 +543,7 @@ SB_EXPORT int sb_add_bias(float* x, const float* bias, int n_rows, int cols, cud
 SB_EXPORT int sb_qk_prepare(const float* sums, int stride, const float* bias, const int* positions, const int* token_row, int H, int G, int D,
                             int dim, const float* q_weight, const float* k_weight, float eps, const float* inv_freq, int rot, void* q_out,
                             int q_stride, void* kc, void* vc, const int* block_table, int bt_width, int ps, int num_pages, int* errors,
-                            int n_tokens, int dtype, cudaStream_t stream) {
+                            int n_tokens, int dtype, int head_norm, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (H <= 0 || G < 0 || D <= 0 || dim <= 0 || dim > D || stride < (H + 2 * G) * D || q_stride < H * D) return SB_ERR_SHAPE;
   if (rot < 0 || (rot & 1) || rot > dim || (rot > 0 && !inv_freq)) return SB_ERR_SHAPE;
@@ -516,11 +558,11 @@ SB_EXPORT int sb_qk_prepare(const float* sums, int stride, const float* bias, co
   if (dtype == SB_DTYPE_F32)
     qk_prepare_kernel<float><<<n_tokens, threads, smem, stream>>>(sums, stride, bias, positions, token_row, H, G, D, dim, q_weight, k_weight, eps,
                                                             inv_freq, rot, (float*)q_out, q_stride, (float*)kc, (float*)vc, block_table,
-                                                            bt_width, ps, num_pages, errors);
+                                                            bt_width, ps, num_pages, errors, head_norm);
   else if (dtype == SB_DTYPE_BF16)
     qk_prepare_kernel<__nv_bfloat16><<<n_tokens, threads, smem, stream>>>(sums, stride, bias, positions, token_row, H, G, D, dim, q_weight, k_weight,
                                                                     eps, inv_freq, rot, (__nv_bfloat16*)q_out, q_stride, (__nv_bfloat16*)kc,
-                                                                    (__nv_bfloat16*)vc, block_table, bt_width, ps, num_pages, errors);
+                                                                    (__nv_bfloat16*)vc, block_table, bt_width, ps, num_pages, errors, head_norm);
   else
     return SB_ERR_DTYPE;
   SB_LAUNCH_CHECK();
@@ -569,7 +611,8 @@ SB_EXPORT int sb_normed_qk_cache_write(void* proj, int stride, const int* positi
 SB_EXPORT int sb_latent_prepare(const void* proj, int stride, int n_q, const int* positions, const int* token_row, const float* c_weight,
                                 float eps, const float* inv_freq, int rot_dims, int H, int dim, int rd, int rank, int D, void* q_lat,
                                 int q_stride, int q_off, void* row_out, int row_stride, void* kc, const int* block_table, int bt_width,
-                                int ps, int num_pages, int write_cache, int* errors, int n_tokens, int dtype, cudaStream_t stream) {
+                                int ps, int num_pages, int write_cache, int* errors, int n_tokens, int dtype, int half_pairs,
+                                cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (H <= 0 || dim <= 0 || rd <= 0 || rank <= 0 || rot_dims < 0 || (rot_dims & 1) || rot_dims > rd || q_off < 0 || D < q_off + rd ||
       q_stride < H * D || n_q != H * (dim + rd) || stride < n_q + rank + rd)
@@ -583,12 +626,12 @@ SB_EXPORT int sb_latent_prepare(const void* proj, int stride, int n_q, const int
     latent_prepare_kernel<float><<<n_tokens, 128, smem, stream>>>((const float*)proj, stride, n_q, positions, token_row, c_weight, eps,
                                                                    inv_freq, rot_dims, H, dim, rd, rank, D, (float*)q_lat, q_stride, q_off,
                                                                    (float*)row_out, row_stride, (float*)kc, block_table, bt_width, ps,
-                                                                   num_pages, write_cache, errors);
+                                                                   num_pages, write_cache, errors, half_pairs);
   else if (dtype == SB_DTYPE_BF16)
     latent_prepare_kernel<__nv_bfloat16><<<n_tokens, 128, smem, stream>>>(
         (const __nv_bfloat16*)proj, stride, n_q, positions, token_row, c_weight, eps, inv_freq, rot_dims, H, dim, rd, rank, D,
         (__nv_bfloat16*)q_lat, q_stride, q_off, (__nv_bfloat16*)row_out, row_stride, (__nv_bfloat16*)kc, block_table, bt_width, ps, num_pages,
-        write_cache, errors);
+        write_cache, errors, half_pairs);
   else
     return SB_ERR_DTYPE;
   SB_LAUNCH_CHECK();
@@ -598,7 +641,7 @@ SB_EXPORT int sb_latent_prepare(const void* proj, int stride, int n_q, const int
 SB_EXPORT int sb_gated_activation(const void* gate_up, void* out, int n_tokens, int inter, int kind, float limit, float alpha, int dtype,
                                   cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
-  if (inter <= 0 || kind < 0 || kind > 1) return SB_ERR_SHAPE;
+  if (inter <= 0 || kind < 0 || kind > 2) return SB_ERR_SHAPE;
   const size_t total = (size_t)n_tokens * inter;
   const int threads = 256;
   if (dtype == SB_DTYPE_BF16 && (inter % 8) == 0 && aligned16(gate_up) && aligned16(out)) {
@@ -619,6 +662,184 @@ SB_EXPORT int sb_gated_activation(const void* gate_up, void* out, int n_tokens, 
                                                                            kind, limit, alpha);
   else
     return SB_ERR_DTYPE;
+  SB_LAUNCH_CHECK();
+  return 0;
+}
+
+// ------------------------------------------------------------------------------------- embedding with a pair table
+namespace {
+
+// One thread per token: the id itself (an id -(s+1) stands for last_token[s]) and the row of the pair table,
+// (previous id * mul_prev + id * mul_cur) mod buckets in 64-bit integers; the sequence's first token (position 0) takes
+// row ``buckets``. The id before a portion's first token is what the request's state slot holds.
+__global__ void __launch_bounds__(128) pair_rows_kernel(const int* __restrict__ tokens, const int* __restrict__ positions,
+                                                        const int* __restrict__ token_row, const int* __restrict__ cu_q,
+                                                        const int* __restrict__ slots, const int* __restrict__ prev_state,
+                                                        long long state_stride, const int* __restrict__ last_token, int n_slots, int vocab,
+                                                        long long mul_prev, long long mul_cur, int buckets, int n_tokens,
+                                                        int* __restrict__ ids, int* __restrict__ rows) {
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= n_tokens) return;
+  auto resolve = [&](int tok) {
+    if (tok < 0 && last_token != nullptr && -tok - 1 < n_slots) tok = last_token[-tok - 1];
+    return tok;
+  };
+  const int r = token_row[t];
+  const int cur = resolve(tokens[t]);
+  ids[t] = cur;
+  int row = buckets;
+  if (positions[t] > 0) {
+    const int prev = t > cu_q[r] ? resolve(tokens[t - 1]) : prev_state[(size_t)slots[r] * state_stride];
+    const bool ok = cur >= 0 && cur < vocab && prev >= 0 && prev < vocab;
+    row = ok ? (int)(((long long)prev * mul_prev + (long long)cur * mul_cur) % (long long)buckets) : buckets;
+  }
+  rows[t] = row;
+}
+
+// One block per token: out = table[id] * scale + pairs[row], both products and the sum in float. The block of a row's last
+// token leaves its id in the request's state slot (every read of the slot happened in the launch before).
+template <typename T>
+__global__ void __launch_bounds__(256) embedding_pair_kernel(const int* __restrict__ ids, const int* __restrict__ rows,
+                                                             const T* __restrict__ table, const T* __restrict__ pairs,
+                                                             float* __restrict__ out, int dim, int vocab, float scale,
+                                                             const int* __restrict__ token_row, const int* __restrict__ cu_q,
+                                                             const int* __restrict__ slots, int* __restrict__ prev_state,
+                                                             long long state_stride) {
+  const int t = blockIdx.x;
+  const int tok = ids[t];
+  const bool ok = tok >= 0 && tok < vocab;
+  const T* src = table + (size_t)(ok ? tok : 0) * dim;
+  const T* add = pairs + (size_t)rows[t] * dim;
+  float* dst = out + (size_t)t * dim;
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) dst[i] = ok ? to_float(src[i]) * scale + to_float(add[i]) : 0.f;
+  if (threadIdx.x == 0) {
+    const int r = token_row[t];
+    if (t == cu_q[r + 1] - 1) prev_state[(size_t)slots[r] * state_stride] = tok;
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) bias_round_kernel(const float* __restrict__ sums, int stride, const float* __restrict__ bias,
+                                                         T* __restrict__ out, int out_stride, int cols, size_t total) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = i / cols;
+    const int c = (int)(i - r * cols);
+    out[r * out_stride + c] = from_float<T>(sums[r * stride + c] + (bias ? bias[c] : 0.f));
+  }
+}
+
+__global__ void __launch_bounds__(256) softcap_kernel(float* __restrict__ x, size_t total, float cap, float inv_cap) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
+    x[i] = cap * tanhf(x[i] * inv_cap);
+}
+
+}  // namespace
+
+// tokens, positions, token_row [T]; cu_q [R + 1]; slots [R]; prev_state: int32 view of a float state, one value per slot,
+// slots state_stride ints apart; table [vocab, dim], pairs [buckets + 1, dim] of ``dtype``; work: 2 T ints; out float [T, dim].
+SB_EXPORT int sb_embedding_pair(const int* tokens, const int* positions, const int* token_row, const int* cu_q, const int* slots,
+                                int* prev_state, long long state_stride, const int* last_token, int n_slots, const void* table,
+                                const void* pairs, int vocab, int dim, int buckets, long long mul_prev, long long mul_cur, float scale,
+                                int* work, float* out, int n_tokens, int dtype, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (dim <= 0 || vocab <= 0 || buckets <= 0 || !prev_state || !work) return SB_ERR_SHAPE;
+  if (mul_prev < 0 || mul_cur < 0 || mul_prev > (1LL << 31) || mul_cur > (1LL << 31)) return SB_ERR_LIMIT;
+  int* ids = work;
+  int* rows = work + n_tokens;
+  pair_rows_kernel<<<(n_tokens + 127) / 128, 128, 0, stream>>>(tokens, positions, token_row, cu_q, slots, prev_state, state_stride,
+                                                               last_token, n_slots, vocab, mul_prev, mul_cur, buckets, n_tokens, ids, rows);
+  SB_LAUNCH_CHECK();
+  const int threads = dim >= 1024 ? 256 : 128;
+  if (dtype == SB_DTYPE_F32)
+    embedding_pair_kernel<float><<<n_tokens, threads, 0, stream>>>(ids, rows, (const float*)table, (const float*)pairs, out, dim, vocab, scale,
+                                                                  token_row, cu_q, slots, prev_state, state_stride);
+  else if (dtype == SB_DTYPE_BF16)
+    embedding_pair_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(ids, rows, (const __nv_bfloat16*)table, (const __nv_bfloat16*)pairs,
+                                                                          out, dim, vocab, scale, token_row, cu_q, slots, prev_state,
+                                                                          state_stride);
+  else
+    return SB_ERR_DTYPE;
+  SB_LAUNCH_CHECK();
+  return 0;
+}
+
+// out [n_rows, cols] (rows out_stride apart) = sums (float, rows stride apart) + bias (float [cols] or null), rounded once.
+SB_EXPORT int sb_bias_round(const float* sums, int stride, const float* bias, void* out, int out_stride, int n_rows, int cols, int dtype,
+                            cudaStream_t stream) {
+  if (n_rows <= 0 || cols <= 0) return 0;
+  if (stride < cols || out_stride < cols) return SB_ERR_SHAPE;
+  const size_t total = (size_t)n_rows * cols, want = (total + 255) / 256;
+  const int blocks = (int)(want < (size_t)sm_count() * 16 ? want : (size_t)sm_count() * 16);
+  if (dtype == SB_DTYPE_F32) bias_round_kernel<float><<<blocks, 256, 0, stream>>>(sums, stride, bias, (float*)out, out_stride, cols, total);
+  else if (dtype == SB_DTYPE_BF16)
+    bias_round_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(sums, stride, bias, (__nv_bfloat16*)out, out_stride, cols, total);
+  else return SB_ERR_DTYPE;
+  SB_LAUNCH_CHECK();
+  return 0;
+}
+
+// x (float, contiguous) <- cap * tanh(x / cap).
+SB_EXPORT int sb_softcap(float* x, long long total, float cap, cudaStream_t stream) {
+  if (total <= 0) return 0;
+  if (!(cap > 0.f)) return SB_ERR_SHAPE;
+  const size_t want = ((size_t)total + 255) / 256;
+  const int blocks = (int)(want < (size_t)sm_count() * 16 ? want : (size_t)sm_count() * 16);
+  softcap_kernel<<<blocks, 256, 0, stream>>>(x, (size_t)total, cap, 1.0f / cap);
+  SB_LAUNCH_CHECK();
+  return 0;
+}
+
+// ------------------------------------------------------------------------------------- residual addition, sigmoid gate
+namespace {
+
+template <typename T>
+__global__ void __launch_bounds__(256) residual_add_kernel(float* __restrict__ x, const T* __restrict__ d, size_t total) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) x[i] += to_float(d[i]);
+}
+
+// out[t, c] = scale * a[t, c] * sigmoid(gate[t, c / per_gate]) (gate null: scale * a), the product in float, rounded once.
+template <typename T>
+__global__ void __launch_bounds__(256) sigmoid_gate_kernel(const T* __restrict__ a, int a_stride, const T* __restrict__ gate, int gate_stride,
+                                                           int per_gate, T* __restrict__ out, int out_stride, int cols, size_t total,
+                                                           float scale) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = i / cols;
+    const int c = (int)(i - r * cols);
+    float v = to_float(a[r * a_stride + c]) * scale;
+    if (gate) v *= 1.f / (1.f + expf(-to_float(gate[r * gate_stride + c / per_gate])));
+    out[r * out_stride + c] = from_float<T>(v);
+  }
+}
+
+}  // namespace
+
+// x (float, contiguous) += d (contiguous, of ``dtype``).
+SB_EXPORT int sb_residual_add(float* x, const void* d, long long total, int dtype, cudaStream_t stream) {
+  if (total <= 0) return 0;
+  const size_t want = ((size_t)total + 255) / 256;
+  const int blocks = (int)(want < (size_t)sm_count() * 16 ? want : (size_t)sm_count() * 16);
+  if (dtype == SB_DTYPE_F32) residual_add_kernel<float><<<blocks, 256, 0, stream>>>(x, (const float*)d, (size_t)total);
+  else if (dtype == SB_DTYPE_BF16) residual_add_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(x, (const __nv_bfloat16*)d, (size_t)total);
+  else return SB_ERR_DTYPE;
+  SB_LAUNCH_CHECK();
+  return 0;
+}
+
+// a, out [n_rows, cols] (row strides given; may be the same buffer), gate [n_rows, gate_cols] or null; gate_cols divides cols.
+SB_EXPORT int sb_sigmoid_gate(const void* a, int a_stride, const void* gate, int gate_stride, int gate_cols, void* out, int out_stride,
+                              int n_rows, int cols, float scale, int dtype, cudaStream_t stream) {
+  if (n_rows <= 0 || cols <= 0) return 0;
+  if (a_stride < cols || out_stride < cols || (gate && (gate_cols <= 0 || cols % gate_cols || gate_stride < gate_cols))) return SB_ERR_SHAPE;
+  const int per_gate = gate ? cols / gate_cols : 1;
+  const size_t total = (size_t)n_rows * cols, want = (total + 255) / 256;
+  const int blocks = (int)(want < (size_t)sm_count() * 16 ? want : (size_t)sm_count() * 16);
+  if (dtype == SB_DTYPE_F32)
+    sigmoid_gate_kernel<float><<<blocks, 256, 0, stream>>>((const float*)a, a_stride, (const float*)gate, gate_stride, per_gate, (float*)out,
+                                                           out_stride, cols, total, scale);
+  else if (dtype == SB_DTYPE_BF16)
+    sigmoid_gate_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)a, a_stride, (const __nv_bfloat16*)gate, gate_stride,
+                                                                   per_gate, (__nv_bfloat16*)out, out_stride, cols, total, scale);
+  else return SB_ERR_DTYPE;
   SB_LAUNCH_CHECK();
   return 0;
 }

@@ -93,7 +93,7 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const float* __restrict_
 template <int PER_LANE>
 __global__ void __launch_bounds__(128) moe_route_bias_kernel(const float* __restrict__ logits, int stride, int E, int top, int score_kind,
                                                              int renorm, float sum_eps, const float* __restrict__ bias, int n_tokens,
-                                                             int* __restrict__ idx, float* __restrict__ wts) {
+                                                             int* __restrict__ idx, float* __restrict__ wts, float weight_scale) {
   const int lane = threadIdx.x & 31;
   const int t = blockIdx.x * 4 + (threadIdx.x >> 5);
   if (t >= n_tokens) return;
@@ -154,7 +154,7 @@ __global__ void __launch_bounds__(128) moe_route_bias_kernel(const float* __rest
   }
   if (lane < top) {
     idx[(size_t)t * top + lane] = chosen;
-    wts[(size_t)t * top + lane] = renorm ? val / (total + sum_eps) : val;
+    wts[(size_t)t * top + lane] = (renorm ? val / (total + sum_eps) : val) * weight_scale;
   }
 }
 
@@ -825,15 +825,16 @@ SB_EXPORT int sb_moe_combine(const float* parts, int top, int n_tokens, int N, v
 }
 
 // As sb_moe_route with more: the row stride of the logits (columns beyond E are not the router's), a float bias [E] or
-// null that joins the scores for the choice only, and sum_eps, added to the sum the chosen scores are divided by.
+// null that joins the scores for the choice only, sum_eps, added to the sum the chosen scores are divided by, and
+// weight_scale, a constant every weight is multiplied by.
 SB_EXPORT int sb_moe_route_bias(const float* logits, int stride, int E, int top, int score_kind, int renorm, float sum_eps,
-                                const float* bias, int n_tokens, int* idx, float* wts, cudaStream_t stream) {
+                                const float* bias, int n_tokens, int* idx, float* wts, float weight_scale, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (E <= 0 || top <= 0 || top > E || top > ROUTE_MAX_TOP || E > 32 * ROUTE_PER_LANE) return SB_ERR_LIMIT;
   if (stride < E) return SB_ERR_SHAPE;
   auto k = E <= 64 ? moe_route_bias_kernel<2> : E <= 128 ? moe_route_bias_kernel<4> : E <= 256 ? moe_route_bias_kernel<8>
                                                                                                : moe_route_bias_kernel<ROUTE_PER_LANE>;
-  k<<<(n_tokens + 3) / 4, 128, 0, stream>>>(logits, stride, E, top, score_kind, renorm, sum_eps, bias, n_tokens, idx, wts);
+  k<<<(n_tokens + 3) / 4, 128, 0, stream>>>(logits, stride, E, top, score_kind, renorm, sum_eps, bias, n_tokens, idx, wts, weight_scale);
   SB_LAUNCH_CHECK();
   return 0;
 }

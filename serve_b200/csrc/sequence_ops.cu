@@ -157,7 +157,9 @@ __global__ void __launch_bounds__(CONV_THREADS) conv_state_kernel(const T* __res
 // tokens' vectors come through a two-stage cp.async ring, REC_TS tokens a stage, so the next tokens arrive while
 // these are worked on; a thread's rows are 4 P apart in fours, so it reads them 16 bytes at a time and the lanes of
 // a column read neighbouring 16 bytes.
-constexpr int MODE_DECAY = 0, MODE_SSM = 1, MODE_DELTA = 2, MODE_WKV = 3;
+constexpr int MODE_DECAY = 0, MODE_SSM = 1, MODE_DELTA = 2, MODE_WKV = 3, MODE_GLA = 4;
+// MODE_GLA: S <- diag(a) S + k v^T, o = S^T q (read out after the update), a = sigmoid(rate + bias)^rate_scale per row of S,
+// formed as exp(-softplus(-(rate + bias)) * rate_scale); q times q_scale.
 constexpr int REC_RPT = 16;
 constexpr int REC_THREADS = 128;
 constexpr int REC_TS = 16;
@@ -178,7 +180,8 @@ struct RecArgs {
   float* out; int out_stride;                        // [T, H * dv] float
   int H, Hqk, dk, dv, P, dkp, dvp, n_tokens;
   float q_scale;
-  // float work space, made by the first kernel: qf, kf [T, Hqk, dkp]; af [T, H, dkp] (DELTA, WKV); vf [T, H, dvp]; sc, dec [T, H]
+  float rate_scale;                                  // GLA: the exponent of the sigmoid (one over the temperature)
+  // float work space, made by the first kernel: qf, kf [T, Hqk, dkp]; af [T, H, dkp] (DELTA, WKV, GLA); vf [T, H, dvp]; sc, dec [T, H]
   float *qf, *kf, *af, *vf, *sc, *dec;
 };
 
@@ -208,6 +211,7 @@ __global__ void __launch_bounds__(REC_THREADS) recurrence_prep_kernel(RecArgs a)
       fq = a.q_scale / sqrtf(sq + 1e-6f);
       fk = 1.f / sqrtf(sk + 1e-6f);
     }
+    if (MODE == MODE_GLA) fq = a.q_scale;
     for (int i = tid; i < dkp; i += 32) {
       float x = 0.f, y = 0.f;
       if (i < dk) {
@@ -240,6 +244,13 @@ __global__ void __launch_bounds__(REC_THREADS) recurrence_prep_kernel(RecArgs a)
         for (int i = tid; i < dkp; i += 32)
           ao[i] = i < dk ? expf(neg_a * softplus_f(load_w(a.rate, a.rate_dtype, r0 + i) + load_w(a.dt_bias, a.par_dtype, (size_t)h * dk + i))) : 1.f;
       }
+    }
+    if (MODE == MODE_GLA) {
+      const size_t r0 = (size_t)t * a.rate_stride + (size_t)h * dk;
+      float* ao = a.af + ((size_t)t * a.H + h) * dkp;
+      for (int i = tid; i < dkp; i += 32)
+        ao[i] = i < dk ? expf(-softplus_f(-(load_w(a.rate, a.rate_dtype, r0 + i) + load_w(a.dt_bias, a.par_dtype, (size_t)h * dk + i))) * a.rate_scale)
+                       : 1.f;
     }
     float bonus_dot = 0.f;
     if (MODE == MODE_WKV) {
@@ -279,8 +290,8 @@ __device__ __forceinline__ void rec_cp4(float* smem, const float* g) {
 // grid (dvp / VC, H, rows); 128 threads; VC = 128 / P columns a block.
 template <int MODE>
 __global__ void __launch_bounds__(REC_THREADS) recurrence_scan_kernel(RecArgs a) {
-  constexpr bool DELTA = MODE == MODE_DELTA, SKIP = MODE == MODE_SSM, WKV = MODE == MODE_WKV;
-  constexpr bool ROWS = DELTA || WKV;                                 // a decay per row of S comes with every token
+  constexpr bool DELTA = MODE == MODE_DELTA, SKIP = MODE == MODE_SSM, WKV = MODE == MODE_WKV, GLA = MODE == MODE_GLA;
+  constexpr bool ROWS = DELTA || WKV || GLA;                               // a decay per row of S comes with every token
   extern __shared__ __align__(16) float smem[];
   const int dk = a.dk, dv = a.dv, P = a.P, dkp = a.dkp, dvp = a.dvp, H = a.H;
   const int VC = REC_THREADS / P;
@@ -377,6 +388,13 @@ __global__ void __launch_bounds__(REC_THREADS) recurrence_scan_kernel(RecArgs a)
         float d = (dot[0] + dot[1]) + (dot[2] + dot[3]);
         for (int o = P >> 1; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
         u = sc * (vv - d);
+      } else if (GLA) {
+#pragma unroll
+        for (int x4 = 0; x4 < 4; ++x4) {
+          const float4 aa = a4[x4 * P + part];
+          s[4 * x4] *= aa.x; s[4 * x4 + 1] *= aa.y; s[4 * x4 + 2] *= aa.z; s[4 * x4 + 3] *= aa.w;
+        }
+        u = vv;
       } else {
 #pragma unroll
         for (int x = 0; x < REC_RPT; ++x) s[x] *= dec;
@@ -411,7 +429,7 @@ static inline int rec_lanes(int dk) {
 
 static inline long long rec_work_floats(int mode, int n_tokens, int H, int Hqk, int dk, int dv) {
   const int P = rec_lanes(dk), dkp = P * REC_RPT, VC = REC_THREADS / P, dvp = (dv + VC - 1) / VC * VC;
-  return (long long)n_tokens * ((long long)2 * Hqk * dkp + ((mode == MODE_DELTA || mode == MODE_WKV) ? (long long)H * dkp : 0) + (long long)H * dvp + 2 * H) + 16;
+  return (long long)n_tokens * ((long long)2 * Hqk * dkp + ((mode == MODE_DELTA || mode == MODE_WKV || mode == MODE_GLA) ? (long long)H * dkp : 0) + (long long)H * dvp + 2 * H) + 16;
 }
 
 template <typename T, int MODE>
@@ -426,7 +444,7 @@ int launch_recurrence(RecArgs a, float* work, int n_rows, cudaStream_t stream) {
   a.qf = work;
   a.kf = a.qf + T_ * a.Hqk * a.dkp;
   a.af = a.kf + T_ * a.Hqk * a.dkp;
-  a.vf = a.af + ((MODE == MODE_DELTA || MODE == MODE_WKV) ? T_ * a.H * a.dkp : 0);
+  a.vf = a.af + ((MODE == MODE_DELTA || MODE == MODE_WKV || MODE == MODE_GLA) ? T_ * a.H * a.dkp : 0);
   a.sc = a.vf + T_ * a.H * a.dvp;
   a.dec = a.sc + T_ * a.H;
   if (a.n_tokens > 0x7fffffff / 1 || a.H > 65535 || a.Hqk > 65535) return SB_ERR_LIMIT;
@@ -435,7 +453,7 @@ int launch_recurrence(RecArgs a, float* work, int n_rows, cudaStream_t stream) {
   if (prep_blocks > 0x7fffffffLL) return SB_ERR_LIMIT;
   recurrence_prep_kernel<T, MODE><<<(unsigned)prep_blocks, REC_THREADS, 0, stream>>>(a);
   SB_LAUNCH_CHECK();
-  const int per_tok = ((MODE == MODE_DELTA || MODE == MODE_WKV) ? 3 : 2) * a.dkp + VC;
+  const int per_tok = ((MODE == MODE_DELTA || MODE == MODE_WKV || MODE == MODE_GLA) ? 3 : 2) * a.dkp + VC;
   const size_t smem = (size_t)2 * (REC_TS * per_tok + 2 * REC_TS) * sizeof(float);
   dim3 grid(a.dvp / VC, a.H, n_rows);
   auto kernel = recurrence_scan_kernel<MODE>;
@@ -745,12 +763,14 @@ SB_EXPORT int sb_linear_recurrence(int mode, const void* q, int q_stride, const 
                                    const void* aux, int aux_stride, const void* rate, int rate_stride, int rate_dtype, int rate_per_head,
                                    const float* bonus, const float* decay, const void* a_log, const void* dt_bias, const void* d_skip, int par_dtype, float* state,
                                    const int* slots, const int* cu_q, float* out, int out_stride, int H, int Hqk, int dk, int dv,
-                                   float q_scale, int n_rows, int n_tokens, float* work, long long state_stride, int dtype, cudaStream_t stream) {
+                                   float q_scale, int n_rows, int n_tokens, float* work, long long state_stride, int dtype, float rate_scale,
+                                   cudaStream_t stream) {
   if (n_rows <= 0 || n_tokens <= 0) return 0;
   if (!work || !aligned16(work)) return SB_ERR_ALIGN;
   if (H <= 0 || Hqk <= 0 || H % Hqk || dk <= 0 || dv <= 0) return SB_ERR_SHAPE;
   if (n_rows > 65535 || H > 65535 || dk > 32 * REC_RPT) return SB_ERR_LIMIT;
   if (mode == MODE_WKV && (H != Hqk || !rate || !dt_bias || !bonus)) return SB_ERR_SHAPE;
+  if (mode == MODE_GLA && (!rate || !dt_bias)) return SB_ERR_SHAPE;
   if (rate && rate_dtype != SB_DTYPE_F32 && rate_dtype != SB_DTYPE_BF16) return SB_ERR_DTYPE;
   RecArgs a;
   a.q = q; a.k = k; a.v = v; a.q_stride = q_stride; a.k_stride = k_stride; a.v_stride = v_stride;
@@ -758,17 +778,19 @@ SB_EXPORT int sb_linear_recurrence(int mode, const void* q, int q_stride, const 
   a.rate_per_head = rate_per_head; a.bonus = bonus; a.decay = decay;
   a.a_log = a_log; a.dt_bias = dt_bias; a.d_skip = d_skip; a.par_dtype = par_dtype; a.state = state; a.state_stride = state_stride; a.slots = slots; a.cu_q = cu_q;
   a.out = out; a.out_stride = out_stride; a.H = H; a.Hqk = Hqk; a.dk = dk; a.dv = dv; a.P = 1; a.dkp = a.dvp = 0; a.n_tokens = n_tokens;
-  a.q_scale = q_scale; a.qf = a.kf = a.af = a.vf = a.sc = a.dec = nullptr;
+  a.q_scale = q_scale; a.rate_scale = rate_scale; a.qf = a.kf = a.af = a.vf = a.sc = a.dec = nullptr;
   if (dtype == SB_DTYPE_F32) {
     if (mode == MODE_DECAY) return launch_recurrence<float, MODE_DECAY>(a, work, n_rows, stream);
     if (mode == MODE_SSM) return launch_recurrence<float, MODE_SSM>(a, work, n_rows, stream);
     if (mode == MODE_DELTA) return launch_recurrence<float, MODE_DELTA>(a, work, n_rows, stream);
     if (mode == MODE_WKV) return launch_recurrence<float, MODE_WKV>(a, work, n_rows, stream);
+    if (mode == MODE_GLA) return launch_recurrence<float, MODE_GLA>(a, work, n_rows, stream);
   } else if (dtype == SB_DTYPE_BF16) {
     if (mode == MODE_DECAY) return launch_recurrence<__nv_bfloat16, MODE_DECAY>(a, work, n_rows, stream);
     if (mode == MODE_SSM) return launch_recurrence<__nv_bfloat16, MODE_SSM>(a, work, n_rows, stream);
     if (mode == MODE_DELTA) return launch_recurrence<__nv_bfloat16, MODE_DELTA>(a, work, n_rows, stream);
     if (mode == MODE_WKV) return launch_recurrence<__nv_bfloat16, MODE_WKV>(a, work, n_rows, stream);
+    if (mode == MODE_GLA) return launch_recurrence<__nv_bfloat16, MODE_GLA>(a, work, n_rows, stream);
   } else {
     return SB_ERR_DTYPE;
   }

@@ -93,8 +93,7 @@ class Engine:
 
     def _make_cache(self) -> None:
         ec = self.engine_config
-        needs = self.model.cache_needs()
-        cache_of = [e.cache_of for e in self.model.schedule]
+        needs, cache_of = self.model.cache_layout()
         num_pages = ec.num_pages
         if num_pages is None:
             # Every group is sized to the same share of the most it could ever use (every slot at full context, or,

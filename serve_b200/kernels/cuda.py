@@ -273,6 +273,52 @@ class CudaKernels:
                                        _DT[table.dtype], _p(last_token), last_token.shape[0] if last_token is not None else 0,
                                        ctypes.c_float(scale), self._s()), "embedding")
 
+    def embedding_pair(self, ctx, table, pairs, state, buckets: int, mul_prev: int, mul_cur: int, out, scale: float = 1.0) -> None:
+        """out[t] = table[token] * scale + pairs[row], row = (previous token * mul_prev + token * mul_cur) mod buckets, or
+        ``buckets`` for a sequence's first token. ``state`` [slots, 1] float holds, as an integer's bits, the last token of
+        every request's previous portion, and takes this portion's."""
+        t = ctx.tokens.shape[0]
+        work = torch.empty(2 * t, dtype=torch.int32, device=out.device)
+        last = getattr(ctx, "last_token", None)
+        self.launches += 2
+        _check(self._prep_lib().sb_embedding_pair(
+            _p(ctx.tokens), _p(ctx.positions), _p(ctx.token_row), _p(ctx.cu_q), _p(ctx.slots), _p(state),
+            ctypes.c_longlong(state.stride(0)), _p(last), last.shape[0] if last is not None else 0, _p(table), _p(pairs), table.shape[0],
+            table.shape[1], int(buckets), ctypes.c_longlong(mul_prev), ctypes.c_longlong(mul_cur), ctypes.c_float(scale), _p(work), _p(out), t,
+            _DT[table.dtype], self._s()), "embedding with a pair table")
+
+    def bias_round(self, sums, bias, out) -> None:
+        """out = sums (float) + bias (float [cols] or None), rounded once to out's type; both may be column slices."""
+        if sums.dtype != torch.float32 or sums.shape != out.shape or sums.stride(1) != 1 or out.stride(1) != 1:
+            raise KernelError("bias_round: float sums and an output of their shape")
+        self.launches += 1
+        _check(self._prep_lib().sb_bias_round(_p(sums), sums.stride(0), _p(bias), _p(out), out.stride(0), sums.shape[0], sums.shape[1],
+                                              _DT[out.dtype], self._s()), "bias")
+
+    def residual_add(self, x, delta) -> None:
+        """x (float residual stream, contiguous) += delta (activations or float, contiguous)."""
+        if x.dtype != torch.float32 or x.shape != delta.shape or not x.is_contiguous() or not delta.is_contiguous():
+            raise KernelError("residual_add: a float stream and a delta of its shape")
+        self.launches += 1
+        _check(self._prep_lib().sb_residual_add(_p(x), _p(delta), ctypes.c_longlong(x.numel()), _DT[delta.dtype], self._s()), "residual addition")
+
+    def sigmoid_gate(self, a, gate, out, scale: float = 1.0) -> None:
+        """out = scale * a * sigmoid(gate): gate [T, g] with g dividing a's columns (one number for each run of columns), or None.
+        a and out may be column slices, and the same buffer."""
+        if a.shape != out.shape or a.dtype != out.dtype or a.stride(1) != 1 or out.stride(1) != 1 or (gate is not None and (gate.dtype != a.dtype or gate.stride(1) != 1)):
+            raise KernelError("sigmoid_gate: operands of one type, contiguous along their rows")
+        self.launches += 1
+        _check(self._prep_lib().sb_sigmoid_gate(_p(a), a.stride(0), _p(gate), gate.stride(0) if gate is not None else 0,
+                                                gate.shape[1] if gate is not None else 0, _p(out), out.stride(0), a.shape[0], a.shape[1],
+                                                ctypes.c_float(scale), _DT[a.dtype], self._s()), "sigmoid gate")
+
+    def softcap(self, x, cap: float) -> None:
+        """x (float, contiguous) <- cap * tanh(x / cap)."""
+        if x.dtype != torch.float32 or not x.is_contiguous():
+            raise KernelError("softcap: float, contiguous")
+        self.launches += 1
+        _check(self._prep_lib().sb_softcap(_p(x), ctypes.c_longlong(x.numel()), ctypes.c_float(cap), self._s()), "capped logits")
+
     def add_rmsnorm(self, x, delta, weight, eps, out) -> None:
         self.launches += 1
         _check(self._core.sb_add_rmsnorm(_p(x), _p(delta), _p(None), _p(weight), _DT[weight.dtype], _p(out), x.shape[0],
@@ -341,11 +387,12 @@ class CudaKernels:
         _check(self._prep_lib().sb_add_bias(_p(x), _p(bias), x.shape[0], x.shape[1], self._s()), "bias")
 
     def qk_prepare(self, sums, bias, positions, token_row, heads, kv_heads, head_dim, dim, q_weight, k_weight, eps, inv_freq, rot_dims,
-                   q_out, k_cache, v_cache, block_table, page_size) -> None:
+                   q_out, k_cache, v_cache, block_table, page_size, head_norm: bool = False) -> None:
         """From the float sums of a fused query | key | value projection [T, (H + 2 G) * D] (heads padded to D; G = 0: queries only):
         bias added, all queries (all keys) of a token divided by their root mean square over H * dim (G * dim) true elements and
         multiplied by float weights laid out like the padded projection (None: no norm), the first rot_dims elements of every
-        query and key head rotated (pairs i, i + rot_dims / 2), queries to q_out, keys and values to their pages."""
+        query and key head rotated (pairs i, i + rot_dims / 2), queries to q_out, keys and values to their pages. ``head_norm``:
+        instead, every query and key head is divided, after its rotation, by its own root mean square over dim elements."""
         if sums.dtype != torch.float32:
             raise KernelError("qk_prepare: the projection's sums are float")
         self.launches += 1
@@ -354,7 +401,7 @@ class CudaKernels:
             _p(sums), sums.stride(0), _p(bias), _p(positions), _p(token_row), heads, kv_heads, head_dim, dim, _p(q_weight), _p(k_weight),
             ctypes.c_float(eps), _p(inv_freq), int(rot_dims), _p(q_out), q_out.stride(0), _p(k_cache if kv_heads else None),
             _p(v_cache if kv_heads else None), _p(block_table), block_table.shape[1], page_size, pages, _p(self.errors_tensor()),
-            sums.shape[0], _DT[q_out.dtype], self._s()), "query/key preparation")
+            sums.shape[0], _DT[q_out.dtype], 1 if head_norm else 0, self._s()), "query/key preparation")
 
     def linear_batched(self, a, w, out) -> None:
         """out[:, b] = a[:, b] @ w[b]^T for every b: a [M, B, K] and out [M, B, N] may be views of wider buffers (unit stride
@@ -370,8 +417,9 @@ class CudaKernels:
                "batched linear")
 
     def gate_up_activation(self, h, w_gate_up, out, activation: str, limit: float = 0.0, alpha: float = 1.0) -> None:
-        """out[T, I] = act(h @ w_gate^T, h @ w_up^T), w_gate_up = [w_gate; w_up]: "swiglu" or "clamped_swish" (g <- min(g, limit),
-        u <- clamp(u, -limit, limit), g * sigmoid(alpha g) * (u + 1)); the product is the library's or the few-rows kernel's."""
+        """out[T, I] = act(h @ w_gate^T, h @ w_up^T), w_gate_up = [w_gate; w_up]: "swiglu", "clamped_swish" (g <- min(g, limit),
+        u <- clamp(u, -limit, limit), g * sigmoid(alpha g) * (u + 1)) or "gelu_tanh" (gelu(g) * u, the tanh form); the product is the
+        library's or the few-rows kernel's."""
         if activation == "swiglu":
             return self.gate_up_swiglu(h, w_gate_up, out)
         t, inter = h.shape[0], out.shape[1]
@@ -394,7 +442,7 @@ class CudaKernels:
         gate_up = torch.empty((t, 2 * inter), dtype=h.dtype, device=h.device)
         self.linear(h, w_gate_up, gate_up)
         self.launches += 1
-        _check(self._prep_lib().sb_gated_activation(_p(gate_up), _p(out), t, inter, {"clamped_swish": 1}[activation], ctypes.c_float(limit),
+        _check(self._prep_lib().sb_gated_activation(_p(gate_up), _p(out), t, inter, {"clamped_swish": 1, "gelu_tanh": 2}[activation], ctypes.c_float(limit),
                                                     ctypes.c_float(alpha), _DT[out.dtype], self._s()), "gated activation")
 
     def normed_qk_cache_write(self, proj, positions, token_row, heads, kv_heads, head_dim, dim, q_weight, k_weight, eps, temp_coef,
@@ -410,18 +458,21 @@ class CudaKernels:
             "query/key norm and cache write")
 
     def latent_prepare(self, proj, n_q, positions, token_row, c_weight, eps, inv_freq, rot_dims, heads, dim, rot_dim, rank, head_dim,
-                       q_lat, k_cache, block_table, page_size, write_cache, q_off=None, row_out=None) -> None:
+                       q_lat, k_cache, block_table, page_size, write_cache, q_off=None, row_out=None,
+                       half_pairs: bool = False) -> None:
         """Latent attention between its input product and its attention: proj [T, >= n_q + rank + rot_dim] holds the heads'
         queries ([dim | rot_dim] each), the latent vector and the shared key part. Writes the cache row [normed latent | rotated
         key part | zeros] (if write_cache), the same row into row_out [T, >= rank + rot_dim] (if given), and columns
-        [q_off, head_dim) of every head of q_lat (rotated query part, zeros); q_off defaults to rank."""
+        [q_off, head_dim) of every head of q_lat (rotated query part, zeros); q_off defaults to rank. Rotated pairs are
+        (2 i, 2 i + 1), or with ``half_pairs`` (i, i + rot_dims / 2)."""
         self.launches += 1
         pages = k_cache.shape[0] if k_cache is not None else 0
         _check(self._prep_lib().sb_latent_prepare(
             _p(proj), proj.stride(0), n_q, _p(positions), _p(token_row), _p(c_weight), ctypes.c_float(eps), _p(inv_freq), rot_dims, heads,
             dim, rot_dim, rank, head_dim, _p(q_lat), q_lat.stride(0), rank if q_off is None else q_off, _p(row_out),
             row_out.stride(0) if row_out is not None else 0, _p(k_cache), _p(block_table), block_table.shape[1], page_size, pages,
-            1 if write_cache else 0, _p(self.errors_tensor()), proj.shape[0], _DT[proj.dtype], self._s()), "latent attention preparation")
+            1 if write_cache else 0, _p(self.errors_tensor()), proj.shape[0], _DT[proj.dtype], 1 if half_pairs else 0, self._s()),
+            "latent attention preparation")
 
     def linear(self, a, w, out) -> None:
         """out[M,N] = a[M,K] @ w[N,K]^T (library matrix product)."""
@@ -860,17 +911,18 @@ class CudaKernels:
 
     def linear_recurrence(self, mode: str, q, k, v, state, ctx, out, heads: int, qk_heads: int, dk: int, dv: int, aux=None, rate=None,
                           decay=None, a_log=None, dt_bias=None, d_skip=None, q_scale: float = 1.0, rate_per_head: bool = False,
-                          bonus=None) -> None:
+                          bonus=None, rate_scale: float = 1.0) -> None:
         """One matrix state [dk, dv] per (request, head), walked over the step's tokens: see csrc/sequence_ops.cu.
         mode "decay": S = decay_h S + k v^T with silu on q, k, v; "ssm": S = exp(-exp(a_log) dt) S + dt k v^T, dt =
         softplus(aux + dt_bias), o += d_skip v; "delta": S = g S, S += k (beta (v - S^T k))^T with g = exp(-exp(a_log)
         softplus(rate + dt_bias)), beta = sigmoid(aux), q and k made unit vectors (``rate_per_head``: rate [T, heads] and dt_bias
         [heads], one decay for a head's whole state); "wkv": o = S^T q + (sum_i q_i bonus_i k_i) v, then S = diag(d) S + k v^T
-        with d = exp(-exp(rate + dt_bias)) per row (rate [T, heads * dk], of a dtype of its own; bonus float [heads * dk]).
+        with d = exp(-exp(rate + dt_bias)) per row (rate [T, heads * dk], of a dtype of its own; bonus float [heads * dk]);
+        "gla": S = diag(a) S + k v^T, o = S^T (q_scale q), a = sigmoid(rate + dt_bias)^rate_scale per row (rate [T, heads * dk]).
         out: float [T, heads * dv]."""
-        par = a_log if a_log is not None else None
+        par = a_log if a_log is not None else (dt_bias if mode == "gla" else None)
         lib = self._seq_lib()
-        code = {"decay": 0, "ssm": 1, "delta": 2, "wkv": 3}[mode]
+        code = {"decay": 0, "ssm": 1, "delta": 2, "wkv": 3, "gla": 4}[mode]
         lib.sb_linear_recurrence_work_floats.restype = ctypes.c_longlong
         need = lib.sb_linear_recurrence_work_floats(code, q.shape[0], heads, qk_heads, dk, dv)
         if need < 0:
@@ -883,7 +935,7 @@ class CudaKernels:
             _DT[rate.dtype] if rate is not None else 0, 1 if rate_per_head else 0, _p(bonus), _p(decay),
             _p(a_log), _p(dt_bias), _p(d_skip), _DT[par.dtype] if par is not None else 0, _p(state), _p(ctx.slots), _p(ctx.cu_q),
             _p(out), out.stride(0), heads, qk_heads, dk, dv, ctypes.c_float(q_scale), ctx.shape.rows, q.shape[0], _p(work),
-            ctypes.c_longlong(state.stride(0)), _DT[v.dtype], self._s()),
+            ctypes.c_longlong(state.stride(0)), _DT[v.dtype], ctypes.c_float(rate_scale), self._s()),
             "linear recurrence")
 
     def gated_norm(self, y, out, groups: int = 0, eps: float = 0.0, weight=None, gate=None, gate_act: str = "sigmoid",
@@ -909,12 +961,13 @@ class CudaKernels:
 
     def routed_experts(self, h, logits, w_gate_up, w_down, top: int, out, score: str = "sigmoid", renormalise: bool = False,
                        scale_input: bool = True, activation: str = "clamped_swish", limit: float = 0.0, alpha: float = 1.702,
-                       outputs=None, choice_bias=None, renormalise_eps: float = 0.0, shared=None, shared_gated: bool = False) -> None:
+                       outputs=None, choice_bias=None, renormalise_eps: float = 0.0, shared=None, shared_gated: bool = False,
+                       weight_scale: float = 1.0) -> None:
         """out[t] = sum over the ``top`` best experts e of expert_e(w_e * h[t]) (or w_e * expert_e(h[t])): logits float [T, E],
         w_gate_up [E, 2 ff, K], w_down [E, N, ff]. More: the router scores the first ``outputs`` columns of logits, of which those
         beyond the E experts stand for the token's input itself; ``choice_bias`` (float [outputs]) joins the scores for the choice
         only; ``renormalise_eps`` joins the sum the weights are divided by; ``shared`` [T, N] is added for every token, times
-        sigmoid(logits[:, outputs]) if ``shared_gated``."""
+        sigmoid(logits[:, outputs]) if ``shared_gated``; every weight is multiplied by ``weight_scale``."""
         lib = self._moe_lib()
         t = logits.shape[0]
         e = w_down.shape[0]
@@ -939,8 +992,8 @@ class CudaKernels:
         self.launches += 4
         if more:
             _check(lib.sb_moe_route_bias(_p(logits), logits.stride(0), outputs, top, {"sigmoid": 0, "softmax": 1}[score],
-                                         1 if renormalise else 0, ctypes.c_float(renormalise_eps), _p(choice_bias), t, _p(idx), _p(wts), s),
-                   "expert choice")
+                                         1 if renormalise else 0, ctypes.c_float(renormalise_eps), _p(choice_bias), t, _p(idx), _p(wts),
+                                         ctypes.c_float(weight_scale), s), "expert choice")
         else:
             _check(lib.sb_moe_route(_p(logits), e, top, {"sigmoid": 0, "softmax": 1}[score], 1 if renormalise else 0, t, _p(idx), _p(wts), s),
                    "expert choice")

@@ -1,3 +1,3 @@
 """Architectures: importing this package registers them."""
-from . import bapavik, lilunex, llama, rogisun  # noqa: F401
+from . import bapavik, gebilorn, lilunex, llama, rogisun  # noqa: F401
 from .decoder import DecoderModel  # noqa: F401

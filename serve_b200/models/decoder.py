@@ -24,6 +24,9 @@ class DecoderModel:
         self.final_norm = build_part("norm", spec.final_norm, runtime)
         self.head = build_part("head", spec.head, runtime)
         self.schedule = list(spec.schedule)
+        # an embedding may keep per-request state too (the token before a portion): its view follows the scheduled entries'
+        need = getattr(self.embedding, "cache_need", None)
+        self._embedding_need = need() if need is not None else None
         self._layer_runs = None     # runs of scheduled layers that one kernel can take whole (found at the first step)
 
     # ---- weights -------------------------------------------------------
@@ -68,6 +71,14 @@ class DecoderModel:
                 needs[e.cache_of] = needs[e.cache_of].covering(self.blocks[e.layer].cache_need())
         return needs
 
+    def cache_layout(self):
+        """(needs, cache_of) for the cache manager: one entry per schedule entry, then one for the embedding if it keeps state."""
+        needs, cache_of = self.cache_needs(), [e.cache_of for e in self.schedule]
+        if self._embedding_need is not None:
+            needs.append(self._embedding_need)
+            cache_of.append(None)
+        return needs, cache_of
+
     # ---- forward -------------------------------------------------------
     def _find_layer_runs(self, cache_views):
         """{first schedule entry: (entry after the last, plan)} for runs of layers that the kernels can run as one launch
@@ -99,7 +110,10 @@ class DecoderModel:
 
     def forward(self, ctx, cache_views):
         """ctx: StepContext. cache_views[i]: CacheView of schedule entry i (or None)."""
-        x = self.embedding.forward(ctx.tokens, ctx)
+        if self._embedding_need is not None:
+            x = self.embedding.forward(ctx.tokens, ctx, cache_views[len(self.schedule)])
+        else:
+            x = self.embedding.forward(ctx.tokens, ctx)
         pending = None
         runs = self._layer_runs
         if runs is None and getattr(self.rt.kernels, "use_layer_runs", False):

@@ -89,3 +89,22 @@ class SandwichNormBlock(Block):
             return x, a
         h = self.feed_forward_norm.forward(x, a, ctx)
         return x, DeferredNorm(self.feed_forward.forward(h, ctx), self.feed_forward_post_norm)
+
+
+@register_part("block", "parallel_residual")
+class ParallelResidualBlock(Block):
+    """One norm whose output both sub-layers read: h = norm(x); x = x + (mixer(h) + ffn(h)). The feed-forward may be left
+    out. The mixer's output joins the float residual stream at once and the feed-forward's travels as the pending delta, so
+    both additions are float."""
+
+    wants = {"norm": "norm", "mixer": "mixer", "feed_forward": "feed_forward"}
+    optional = ("feed_forward",)
+
+    def forward(self, x, pending, ctx, cache):
+        h = self.norm.forward(x, pending, ctx)
+        a = self.mixer.forward(h, ctx, cache)
+        if self.feed_forward is None:
+            return x, a
+        f = self.feed_forward.forward(h, ctx)
+        self.rt.kernels.residual_add(x, a)
+        return x, f

@@ -9,7 +9,7 @@ from __future__ import annotations
 
 import torch
 
-from .base import Part, TensorDecl, register_part
+from .base import CacheNeed, Part, TensorDecl, register_part
 
 
 @register_part("embedding", "table")
@@ -39,9 +39,46 @@ class TokenEmbedding(Part):
         return x
 
 
+@register_part("embedding", "pair_table")
+class PairTableEmbedding(TokenEmbedding):
+    """The token's row times ``scale`` plus a row of a second table chosen by the token together with the one before it:
+    row (previous id * mul_prev + id * mul_cur) mod buckets, and row ``buckets`` (the table's last) for a sequence's first
+    token. The id before a portion's first token is per-request state: one number per slot, kept as an integer's bits
+    in the float state pool. params: vocab, hidden, name, scale, pairs {name, buckets, mul_prev, mul_cur}."""
+
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        pairs = spec.params["pairs"]
+        self.pairs_name = self.prefix + pairs.get("name", "pairs")
+        self.buckets, self.mul_prev, self.mul_cur = int(pairs["buckets"]), int(pairs["mul_prev"]), int(pairs["mul_cur"])
+        if self.buckets <= 0 or self.mul_prev < 0 or self.mul_cur < 0:
+            raise ValueError("pair_table: buckets must be positive and the multipliers not negative")
+        self.pairs = None
+
+    def kernel_needs(self):
+        return {"libraries": ["prep"]}
+
+    def tensor_decls(self):
+        return super().tensor_decls() + [TensorDecl(self.pairs_name, (self.buckets + 1, self.hidden))]
+
+    def load(self, tensors):
+        super().load(tensors)
+        self.pairs = tensors[self.pairs_name]
+
+    def cache_need(self):
+        return CacheNeed(states=(("previous_token", (1,)),))
+
+    def forward(self, tokens, ctx, cache=None):
+        x = torch.empty((tokens.shape[0], self.hidden), dtype=torch.float32, device=self.rt.device)
+        self.rt.kernels.embedding_pair(ctx, self.table, self.pairs, cache.states["previous_token"], self.buckets, self.mul_prev,
+                                       self.mul_cur, x, scale=self.scale)
+        return x
+
+
 @register_part("head", "linear")
 class OutputHead(Part):
-    """params: vocab, hidden, name; tied_to: name of the embedding table, or None."""
+    """params: vocab, hidden, name; tied_to: name of the embedding table, or None; softcap c (None: none): the logits
+    become c * tanh(logits / c)."""
 
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
@@ -50,7 +87,11 @@ class OutputHead(Part):
         self.tied_to = spec.params.get("tied_to")
         self.own_name = self.prefix + spec.params.get("name", "weight")
         self.name = self.tied_to if self.tied_to else self.own_name
+        self.softcap = float(spec.params["softcap"]) if spec.params.get("softcap") else 0.0
         self.weight = None
+
+    def kernel_needs(self):
+        return {"libraries": ["prep"]} if self.softcap else {}
 
     def tensor_decls(self):
         return [TensorDecl(self.name, (self.vocab, self.hidden))]
@@ -64,4 +105,6 @@ class OutputHead(Part):
     def forward(self, h, ctx):
         logits = torch.empty((h.shape[0], self.vocab), dtype=torch.float32, device=self.rt.device)
         self.rt.kernels.linear(h, self.weight, logits)
+        if self.softcap:
+            self.rt.kernels.softcap(logits, self.softcap)
         return logits

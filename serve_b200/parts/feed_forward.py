@@ -56,20 +56,24 @@ class SwiGLU(FeedForward):
 @register_part("feed_forward", "gated_dense")
 class GatedDense(SwiGLU):
     """The same three matrices with the activation as a parameter. params: hidden, intermediate, names, activation
-    ("swiglu" | "clamped_swish"), limit, alpha. clamped_swish: g <- min(g, limit), u <- clamp(u, -limit, limit),
-    g * sigmoid(alpha g) * (u + 1), computed in float32 on the float sums of the product where that is fused."""
+    ("swiglu" | "clamped_swish" | "gelu_tanh"), limit, alpha. clamped_swish: g <- min(g, limit), u <- clamp(u, -limit, limit),
+    g * sigmoid(alpha g) * (u + 1), computed in float32 on the float sums of the product where that is fused. gelu_tanh:
+    0.5 g (1 + tanh(sqrt(2 / pi) (g + 0.044715 g^3))) * u."""
 
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
         p = spec.params
         self.activation = p.get("activation", "swiglu")
-        if self.activation not in ("swiglu", "clamped_swish"):
-            raise ValueError(f"gated_dense: activation {self.activation!r} is not known (swiglu, clamped_swish)")
+        if self.activation not in ("swiglu", "clamped_swish", "gelu_tanh"):
+            raise ValueError(f"gated_dense: activation {self.activation!r} is not known (swiglu, clamped_swish, gelu_tanh)")
         self.limit = float(p.get("limit") or 0.0)
         self.alpha = float(p.get("alpha") or 1.0)
 
     def fused_description(self):
         return None if self.activation != "swiglu" else super().fused_description()
+
+    def kernel_needs(self):
+        return {"libraries": ["prep"]} if self.activation != "swiglu" else {}
 
     def forward(self, h, ctx):
         if self.activation == "swiglu":

@@ -14,6 +14,10 @@ attention is one over a single shared key/value head whose keys and values are t
 output per head, sum_j p_j c_j, then goes through V_n and the output projection. Both per-head products are batched
 library products. The cache's value tensor is its key tensor (``CacheNeed.shared_kv``).
 
+With ``q_rank`` the queries come through a low-rank step of their own: c_q = W_dq h ("dq" [q_rank, hidden]) divided by its
+root mean square and multiplied by a weight ("dq.norm"), then q = W_uq c_q ("uq" [heads * (dim + rot_dim), q_rank]); there
+is no "q" tensor then. ``pairing`` "half" rotates pairs (i, i + rot_dims / 2) instead of neighbours.
+
 The attention kernels' rows end at 256 numbers. A model whose kv_rank + rot_dim is larger runs the other way round: every
 head's key [U_n c | rotated part] and value V_n c are read out when the token arrives and cached in ordinary pages, one
 key/value head per query head (``per_head``; more cache, the same results).
@@ -31,6 +35,7 @@ from .base import CacheNeed, Mixer, TensorDecl, register_part
 @register_part("mixer", "latent_attention")
 class LatentAttention(Mixer):
     """params: hidden, heads, dim, rot_dim, vdim, kv_rank, scale, rot_base, rot_dims (default rot_dim), eps, window (None), names,
+    q_rank (None: queries straight from the input), pairing ("interleaved" | "half"), rot_scaling (as the rotary part's, or None),
     per_head (default: only when kv_rank + rot_dim exceeds the attention kernels' widest row)."""
 
     MAX_ROW = 256        # the widest head the attention kernels take
@@ -46,6 +51,11 @@ class LatentAttention(Mixer):
         if self.rot_dims % 2 or self.rot_dims > self.rot_dim:
             raise ValueError(f"rot_dims {self.rot_dims} must be even and at most rot_dim {self.rot_dim}")
         self.eps = float(p["eps"])
+        self.q_rank = int(p["q_rank"]) if p.get("q_rank") else 0
+        if p.get("pairing", "interleaved") not in ("interleaved", "half"):
+            raise ValueError(f"latent_attention: pairing {p['pairing']!r} is not known (interleaved, half)")
+        self.half_pairs = p.get("pairing", "interleaved") == "half"
+        self.rot_scaling = p.get("rot_scaling")
         self.window = int(p["window"]) if p.get("window") else None
         self.names = dict(p.get("names", {}))
         self.row = self.rank + self.rot_dim                       # what a token leaves in the cache
@@ -64,10 +74,14 @@ class LatentAttention(Mixer):
         return self.prefix + self.names.get(key, key)
 
     def kernel_needs(self):
-        return {"attention_head_dims": [self.head_dim], "libraries": ["prep"]}
+        return {"attention_head_dims": [self.head_dim], "libraries": ["prep"] + (["seq"] if self.q_rank else [])}
 
     def tensor_decls(self):
-        return [TensorDecl(self._name("q"), (self.heads * (self.dim + self.rot_dim), self.hidden)),
+        n_q = self.heads * (self.dim + self.rot_dim)
+        queries = [TensorDecl(self._name("q"), (n_q, self.hidden))] if not self.q_rank else [
+            TensorDecl(self._name("dq"), (self.q_rank, self.hidden)), TensorDecl(self._name("dq.norm"), (self.q_rank,), role="vector", init="norm"),
+            TensorDecl(self._name("uq"), (n_q, self.q_rank))]
+        return queries + [
                 TensorDecl(self._name("dkv"), (self.row, self.hidden)),
                 TensorDecl(self._name("dkv.norm"), (self.rank,), role="vector", init="norm"),
                 TensorDecl(self._name("uk"), (self.heads * self.dim, self.rank)),
@@ -76,11 +90,18 @@ class LatentAttention(Mixer):
 
     def load(self, tensors):
         # one product for q and the down projection; its row count is padded to a multiple of 8 (16-byte rows in bfloat16)
-        w = torch.cat([tensors[self._name("q")], tensors[self._name("dkv")]], dim=0)
         self.n_q = self.heads * (self.dim + self.rot_dim)
-        self.n_in = 8 * -(-w.shape[0] // 8)
-        if self.n_in != w.shape[0]:
-            w = torch.cat([w, w.new_zeros((self.n_in - w.shape[0], w.shape[1]))], dim=0)
+        if self.q_rank:
+            # the input's product gives [latent | shared key part | query latent]; the queries' second step fills the columns before
+            w = torch.cat([tensors[self._name("dkv")], tensors[self._name("dq")]], dim=0)
+            self.n_in = 8 * -(-(self.n_q + w.shape[0]) // 8)
+            self.w_uq = tensors[self._name("uq")].contiguous()
+            self.q_norm = tensors[self._name("dq.norm")].float().contiguous()
+        else:
+            w = torch.cat([tensors[self._name("q")], tensors[self._name("dkv")]], dim=0)
+            self.n_in = 8 * -(-w.shape[0] // 8)
+            if self.n_in != w.shape[0]:
+                w = torch.cat([w, w.new_zeros((self.n_in - w.shape[0], w.shape[1]))], dim=0)
         self.w_in = w.contiguous()
         self.c_norm = tensors[self._name("dkv.norm")].float().contiguous()
         # U_n^T as the [N, K] operand of out = a @ w^T: [heads, kv_rank, dim]
@@ -94,8 +115,13 @@ class LatentAttention(Mixer):
                 padded[:, :, : self.vdim] = w_o.view(self.hidden, self.heads, self.vdim)
                 w_o = padded.view(self.hidden, self.heads * self.head_dim)
         self.w_o = w_o.contiguous()
-        i = torch.arange(self.rot_dims // 2, dtype=torch.float64)
-        self.inv_freq = (self.rot_base ** (-2.0 * i / self.rot_dims)).to(torch.float32).to(self.w_o.device)
+        if self.rot_scaling:
+            from .rotary import rotary_inv_freq
+
+            self.inv_freq = rotary_inv_freq(self.rot_dims, self.rot_base, self.rot_scaling).to(self.w_o.device)
+        else:
+            i = torch.arange(self.rot_dims // 2, dtype=torch.float64)
+            self.inv_freq = (self.rot_base ** (-2.0 * i / self.rot_dims)).to(torch.float32).to(self.w_o.device)
 
     def cache_need(self):
         if self.per_head:
@@ -111,13 +137,21 @@ class LatentAttention(Mixer):
         k = self.rt.kernels
         t, d = h.shape[0], self.head_dim
         proj = self.rt.empty_act((t, self.n_in))
-        k.linear(h, self.w_in, proj)
+        if self.q_rank:
+            at = self.n_q + self.row
+            k.linear(h, self.w_in, proj[:, self.n_q: at + self.q_rank])
+            cq = self.rt.empty_act((t, self.q_rank))
+            k.gated_norm(proj[:, at: at + self.q_rank], cq, groups=1, eps=self.eps, weight=self.q_norm)
+            k.linear(cq, self.w_uq, proj[:, : self.n_q])
+        else:
+            k.linear(h, self.w_in, proj)
         table = ctx.block_tables[cache.group]
         if self.per_head:
             return self._mix_per_head(proj, ctx, cache, table, out)
         q_lat = self.rt.empty_act((t, self.heads * d))             # per head [U^T q_plain | q_rot | zeros]
         k.latent_prepare(proj, self.n_q, ctx.positions, ctx.token_row, self.c_norm, self.eps, self.inv_freq, self.rot_dims, self.heads,
-                         self.dim, self.rot_dim, self.rank, d, q_lat, cache.k, table, cache.page_size, cache.writes)
+                         self.dim, self.rot_dim, self.rank, d, q_lat, cache.k, table, cache.page_size, cache.writes,
+                         **({"half_pairs": True} if self.half_pairs else {}))
         q3 = proj[:, : self.n_q].view(t, self.heads, self.dim + self.rot_dim)
         k.linear_batched(q3[:, :, : self.dim], self.w_uk_t, q_lat.view(t, self.heads, d)[:, :, : self.rank])
         o_lat = self.rt.empty_act((t, self.heads * d))
@@ -133,7 +167,8 @@ class LatentAttention(Mixer):
         qkv = torch.zeros((t, 3 * hh * d), dtype=proj.dtype, device=proj.device)
         row = self.rt.empty_act((t, 8 * -(-self.row // 8)))
         k.latent_prepare(proj, self.n_q, ctx.positions, ctx.token_row, self.c_norm, self.eps, self.inv_freq, self.rot_dims, hh, self.dim,
-                         self.rot_dim, self.rank, d, qkv, None, table, cache.page_size, False, q_off=self.dim, row_out=row)
+                         self.rot_dim, self.rank, d, qkv, None, table, cache.page_size, False, q_off=self.dim, row_out=row,
+                         **({"half_pairs": True} if self.half_pairs else {}))
         q3 = qkv.view(t, 3 * hh, d)
         q3[:, :hh, : self.dim].copy_(proj[:, : self.n_q].view(t, hh, self.dim + self.rot_dim)[:, :, : self.dim])
         c = row[:, None, : self.rank].expand(t, hh, self.rank)

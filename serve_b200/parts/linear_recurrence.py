@@ -10,6 +10,8 @@ All of them keep S [dk, dv] per (request, head) in float and differ in how a tok
   "wkv"          o = (S + diag(u_h) k v^T)^T r;  S <- diag(d) S + k v^T      r, k, v, the gate and the decay each read
                  their own blend of the token's input with the one before; d = exp(-exp(w0 + W2 tanh(W1 x_w))) per key
                  channel; the bonus u_h counts for the current token only, and the read-out comes before the update
+  "gated_linear_attention"  S <- diag(a) S + k v^T,  o = S^T q      q times dk^-1/2; a = sigmoid(W_a2 (W_a1 h) + b)^(1/tau) per key
+                 channel, formed in float as exp(log_sigmoid(z) / tau); the read-out comes after the update
 
 The read-out goes through a root-mean-square norm with a gate (parts/gated_norm.py) and an output projection.
 One kernel walks the tokens of every request of the step in order (csrc/sequence_ops.cu), so a prompt cut into
@@ -291,3 +293,67 @@ class WkvMixer(RecurrentMixer):
         k.linear_recurrence("wkv", proj[:, 0], proj[:, 1], proj[:, 2], cache.states["state"], ctx, y, self.heads, self.heads, self.dim,
                             self.dim, rate=rate, dt_bias=self.w0, bonus=self.bonus)
         self.norm.forward(y, proj[:, 3], out, scale)
+
+
+@register_part("mixer", "gated_linear_attention")
+class GatedLinearAttention(RecurrentMixer):
+    """params: hidden, heads, dim, vdim, tau, eps, rank (width of the decay's two-step projection; None: whatever the
+    weight file has). Tensors: "q", "k" [heads * dim, hidden], "v", "g" [heads * vdim, hidden], "a1" [rank, hidden], "a2"
+    [heads * dim, rank], "a2.b" [heads * dim], "norm" [vdim] (one weight for every head), "o". The read-out is divided by
+    its root mean square per head, multiplied by the weight and by silu(W_g h)."""
+
+    def __init__(self, spec, runtime):
+        super().__init__(spec, runtime)
+        p = spec.params
+        self._common(p)
+        self.dim, self.vdim, self.tau = int(p["dim"]), int(p["vdim"]), float(p["tau"])
+        if not self.tau > 0:
+            raise ValueError("gated_linear_attention: tau must be positive")
+        self.rank = int(p["rank"]) if p.get("rank") else -1
+        self.qk, self.mixed_size = self.heads * self.dim, self.heads * self.vdim
+        self.norm = build_part("norm", PartSpec("gated_group_rms", {
+            "channels": self.mixed_size, "groups": self.heads, "eps": self.eps, "weight_size": self.vdim,
+            "weight_name": self.names.get("norm", "norm"), "gate": "silu"}, self.prefix), runtime)
+
+    def kernel_needs(self):
+        return {"libraries": ["seq"]}
+
+    def tensor_decls(self):
+        hid = self.hidden
+        return ([TensorDecl(self._name("q"), (self.qk, hid)), TensorDecl(self._name("k"), (self.qk, hid)),
+                 TensorDecl(self._name("v"), (self.mixed_size, hid)), TensorDecl(self._name("g"), (self.mixed_size, hid)),
+                 TensorDecl(self._name("a1"), (self.rank, hid)), TensorDecl(self._name("a2"), (self.qk, self.rank)),
+                 TensorDecl(self._name("a2.b"), (self.qk,), role="vector", init="small"),
+                 TensorDecl(self._name("o"), (hid, self.mixed_size))] + self.norm.tensor_decls())
+
+    def load(self, tensors):
+        t = lambda n: tensors[self._name(n)]
+        if t("a1").shape[0] != t("a2").shape[1]:
+            raise ValueError(f"{self.prefix}: the two steps of the decay's projection do not fit each other")
+        self.rank_a = t("a1").shape[0]
+        # one product for q, k, v, the gate and the decay's first step (its rows padded to a multiple of 8 with zeros)
+        pad = -self.rank_a % 8
+        a1 = torch.cat([t("a1"), t("a1").new_zeros((pad, self.hidden))], 0) if pad else t("a1")
+        self.w_in = torch.cat([t("q"), t("k"), t("v"), t("g"), a1], dim=0).contiguous()
+        a2 = torch.cat([t("a2"), t("a2").new_zeros((self.qk, pad))], 1) if pad else t("a2")
+        self.w_a2 = a2.contiguous()
+        self.rank_p = self.rank_a + pad
+        self.b_a2 = t("a2.b").float().contiguous()
+        self.w_o = t("o").contiguous()
+        self.norm.load(tensors)
+
+    def cache_need(self):
+        return CacheNeed(states=(("state", (self.heads, self.dim, self.vdim)),))
+
+    def mix_into(self, h, ctx, cache, out, scale: float = 1.0):
+        k = self.rt.kernels
+        t, hk, hv = h.shape[0], self.qk, self.mixed_size
+        proj = self.rt.empty_act((t, 2 * hk + 2 * hv + self.rank_p))
+        k.linear(h, self.w_in, proj)
+        rate = torch.empty((t, hk), dtype=torch.float32, device=h.device)     # float sums: what enters the recurrence is not rounded
+        k.linear(proj[:, 2 * hk + 2 * hv:], self.w_a2, rate)
+        y = self._readout(t)
+        k.linear_recurrence("gla", proj[:, :hk], proj[:, hk: 2 * hk], proj[:, 2 * hk: 2 * hk + hv], cache.states["state"], ctx, y,
+                            self.heads, self.heads, self.dim, self.vdim, rate=rate, dt_bias=self.b_a2,
+                            q_scale=1.0 / math.sqrt(self.dim), rate_scale=1.0 / self.tau)
+        self.norm.forward(y, proj[:, 2 * hk + hv: 2 * hk + 2 * hv], out, scale)

@@ -13,20 +13,24 @@ from .base import DeferredNorm, Norm, TensorDecl, plain_delta, register_part
 
 @register_part("norm", "rms")
 class RMSNorm(Norm):
-    """params: size, eps, weight_name (relative to prefix, default "weight")."""
+    """params: size, eps, weight_name (relative to prefix, default "weight"), offset (default 0: the stored weight is its
+    distance from ``offset``, so the factor is offset + w, formed once at load in float)."""
 
     def __init__(self, spec, runtime):
         super().__init__(spec, runtime)
         self.size = int(spec.params["size"])
         self.eps = float(spec.params["eps"])
         self.weight_name = self.prefix + spec.params.get("weight_name", "weight")
+        self.offset = float(spec.params.get("offset") or 0.0)
         self.weight = None
 
     def tensor_decls(self):
-        return [TensorDecl(self.weight_name, (self.size,), role="vector", init="norm")]
+        return [TensorDecl(self.weight_name, (self.size,), role="vector", init="small" if self.offset else "norm")]
 
     def load(self, tensors):
         self.weight = tensors[self.weight_name]
+        if self.offset:
+            self.weight = (self.weight.float() + self.offset).contiguous()
 
     def fused_description(self):
         """What a kernel that runs whole layers at once needs to know of this norm."""

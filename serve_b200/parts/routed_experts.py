@@ -6,7 +6,8 @@ weight multiplies the expert's input (``scale_input``), which matters because th
 output. Options: ``correction``, a learned float per router output that is added to the scores for the choice only (the
 weights use the scores without it); ``identity``, that many more router outputs after the experts' whose "expert" is
 the token's input itself (no tensors); ``shared``, one more gated feed-forward of its own width that every token goes
-through, its output multiplied by sigmoid(w_sg . h) if ``gated``. Expert activations: "clamped_swish": g = min(gate, limit), u = clamp(up, -limit, limit), g * sigmoid(alpha g)
+through, its output multiplied by sigmoid(w_sg . h) if ``gated``; ``weight_scale``, a constant every weight is multiplied
+by. Expert activations: "clamped_swish": g = min(gate, limit), u = clamp(up, -limit, limit), g * sigmoid(alpha g)
 * (u + 1); "swiglu": silu(gate) * up. The experts' matrices are stacked at load into [E, 2 ff, hidden] (gate rows,
 then up rows) and [E, hidden, ff]; tokens are grouped by expert on the device, so a step has no host round trip
 (csrc/routed_experts.cu).
@@ -22,7 +23,7 @@ from .base import FeedForward, TensorDecl, build_part, register_part
 @register_part("feed_forward", "routed_experts")
 class RoutedExperts(FeedForward):
     """params: hidden, experts, top, ff, score ("sigmoid" | "softmax"), renormalise, renormalise_eps (added to the sum),
-    scale_input, activation, limit, alpha, correction (bool), identity (count), shared ({ff, gated} or None),
+    scale_input, activation, limit, alpha, correction (bool), identity (count), shared ({ff, gated} or None), weight_scale,
     names: router, correction, shared (prefix), shared_gate, and expert tensor names as patterns with {e} (defaults "router",
     "correction", "shared.", "shared.sg", "e{e}.gate", "e{e}.up", "e{e}.down")."""
 
@@ -38,6 +39,7 @@ class RoutedExperts(FeedForward):
         self.renormalise = bool(p.get("renormalise", False))
         self.renormalise_eps = float(p.get("renormalise_eps") or 0.0)
         self.correction = bool(p.get("correction", False))
+        self.weight_scale = float(p["weight_scale"]) if p.get("weight_scale") is not None else 1.0
         shared = p.get("shared")
         self.shared_gated = bool(shared and shared.get("gated"))
         self.scale_input = bool(p.get("scale_input", True))
@@ -56,7 +58,7 @@ class RoutedExperts(FeedForward):
             sp = self.prefix + names.get("shared", "shared.")
             self.shared = build_part("feed_forward", PartSpec("swiglu", {"hidden": self.hidden, "intermediate": int(shared["ff"]),
                                                                          "names": {"gate": "gate", "up": "up", "down": "down"}}, sp), runtime)
-        self.plain = not (self.identity or self.correction or self.shared or self.renormalise_eps)
+        self.plain = not (self.identity or self.correction or self.shared or self.renormalise_eps or self.weight_scale != 1.0)
         self.w_router = self.w_gate_up = self.w_down = self.choice_bias = None
 
     def kernel_needs(self):
@@ -101,7 +103,8 @@ class RoutedExperts(FeedForward):
         rt.kernels.routed_experts(h, logits, self.w_gate_up, self.w_down, self.top, out, score=self.score, renormalise=self.renormalise,
                                   scale_input=self.scale_input, activation=self.activation, limit=self.limit, alpha=self.alpha,
                                   outputs=self.outputs, choice_bias=self.choice_bias, renormalise_eps=self.renormalise_eps,
-                                  shared=shared, shared_gated=self.shared_gated)
+                                  shared=shared, shared_gated=self.shared_gated,
+                                  **({"weight_scale": self.weight_scale} if self.weight_scale != 1.0 else {}))
         return out
 
 

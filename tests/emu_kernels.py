@@ -44,6 +44,35 @@ class EmuKernels:
     def embedding(self, tokens, table, out, last_token=None, scale=1.0):
         out.copy_((table[self._ids(tokens, last_token)].to(torch.float32) * scale).to(out.dtype))
 
+    def embedding_pair(self, ctx, table, pairs, state, buckets, mul_prev, mul_cur, out, scale=1.0):
+        ids = self._ids(ctx.tokens, getattr(ctx, "last_token", None))
+        cu, pos = ctx.cu_q.tolist(), ctx.positions.tolist()
+        held = state.view(torch.int32)
+        rows = []
+        for r, slot in enumerate(ctx.slots.tolist()):
+            for t in range(cu[r], cu[r + 1]):
+                prev = int(ids[t - 1]) if t > cu[r] else int(held[slot, 0])
+                rows.append(buckets if pos[t] == 0 else (prev * mul_prev + int(ids[t]) * mul_cur) % buckets)
+            if cu[r + 1] > cu[r]:
+                held[slot, 0] = int(ids[cu[r + 1] - 1])
+        rows = torch.tensor(rows, dtype=torch.long, device=out.device)
+        out.copy_((table[ids].to(torch.float32) * scale + pairs[rows].to(torch.float32)).to(out.dtype))
+
+    def bias_round(self, sums, bias, out):
+        out.copy_((sums if bias is None else sums + bias.to(sums.dtype)).to(out.dtype))
+
+    def residual_add(self, x, delta):
+        x.add_(delta.to(x.dtype))
+
+    def sigmoid_gate(self, a, gate, out, scale=1.0):
+        v = a.to(self.math) * scale
+        if gate is not None:
+            v = v * torch.sigmoid(gate.to(self.math)).repeat_interleave(a.shape[1] // gate.shape[1], 1)
+        out.copy_(v.to(out.dtype))
+
+    def softcap(self, x, cap):
+        x.copy_(cap * torch.tanh(x / cap))
+
     def _layer_norm(self, v, weight, eps):
         v = v.to(self.math)
         d = v - v.mean(-1, keepdim=True)
@@ -128,6 +157,8 @@ class EmuKernels:
         if activation == "clamped_swish":
             g, u = torch.clamp(g, max=limit), torch.clamp(u, -limit, limit)
             out.copy_((g * torch.sigmoid(alpha * g) * (u + 1)).to(out.dtype))
+        elif activation == "gelu_tanh":
+            out.copy_((torch.nn.functional.gelu(g, approximate="tanh") * u).to(out.dtype))
         else:
             out.copy_((g * torch.sigmoid(g) * u).to(out.dtype))
 
@@ -189,7 +220,7 @@ class EmuKernels:
         x.add_(bias.to(x.dtype))
 
     def qk_prepare(self, sums, bias, positions, token_row, heads, kv_heads, head_dim, dim, q_weight, k_weight, eps, inv_freq, rot_dims,
-                   q_out, k_cache, v_cache, block_table, page_size):
+                   q_out, k_cache, v_cache, block_table, page_size, head_norm=False):
         t, d, m = sums.shape[0], head_dim, self.math
         x = sums.to(m)
         if bias is not None:
@@ -208,6 +239,8 @@ class EmuKernels:
                 a, b = v[..., :half].clone(), v[..., half: rot_dims].clone()
                 v[..., :half] = a * cos - b * sin
                 v[..., half: rot_dims] = b * cos + a * sin
+            if head_norm:
+                v = v * torch.rsqrt(v.pow(2).sum(-1, keepdim=True) / dim + eps)
             return v
 
         q_out.copy_(prepare(x[:, :heads], heads, q_weight).reshape(t, heads * d).to(q_out.dtype))
@@ -242,15 +275,18 @@ class EmuKernels:
             self._write_pages(v_cache, x[:, heads + kv_heads:], positions, token_row, block_table, page_size)
 
     def latent_prepare(self, proj, n_q, positions, token_row, c_weight, eps, inv_freq, rot_dims, heads, dim, rot_dim, rank, head_dim,
-                       q_lat, k_cache, block_table, page_size, write_cache, q_off=None, row_out=None):
+                       q_lat, k_cache, block_table, page_size, write_cache, q_off=None, row_out=None, half_pairs=False):
         t, m = proj.shape[0], self.math
         ang = positions.to(torch.float32)[:, None] * inv_freq.to(torch.float32)[None, :]
         cos, sin = ang.cos().to(m), ang.sin().to(m)
 
         def rotate(v):                      # [..., rot_dim] with t leading
-            a, b = v[..., 0:rot_dims:2], v[..., 1:rot_dims:2]
             shape = (t,) + (1,) * (v.dim() - 2) + (rot_dims // 2,)
             c, s = cos.view(shape), sin.view(shape)
+            if half_pairs:
+                a, b = v[..., : rot_dims // 2], v[..., rot_dims // 2: rot_dims]
+                return torch.cat([a * c - b * s, b * c + a * s, v[..., rot_dims:]], -1)
+            a, b = v[..., 0:rot_dims:2], v[..., 1:rot_dims:2]
             return torch.cat([torch.stack([a * c - b * s, b * c + a * s], -1).flatten(-2), v[..., rot_dims:]], -1)
 
         q = proj[:, :n_q].view(t, heads, dim + rot_dim).to(m)
@@ -349,7 +385,7 @@ class EmuKernels:
                 state[slot] = seq[-k:].to(state.dtype)
 
     def linear_recurrence(self, mode, q, k, v, state, ctx, out, heads, qk_heads, dk, dv, aux=None, rate=None, decay=None,
-                          a_log=None, dt_bias=None, d_skip=None, q_scale=1.0, rate_per_head=False, bonus=None):
+                          a_log=None, dt_bias=None, d_skip=None, q_scale=1.0, rate_per_head=False, bonus=None, rate_scale=1.0):
         m = self.math
         f = torch.nn.functional
         cu = ctx.cu_q.tolist()
@@ -372,6 +408,10 @@ class EmuKernels:
             elif mode == "wkv":
                 dec = torch.exp(-torch.exp(rate[a:b, : heads * dk].to(m) + dt_bias.to(m))).reshape(n, heads, dk)
                 extra = bonus.to(m).reshape(heads, dk)
+            elif mode == "gla":
+                qq = qq * q_scale
+                dec = torch.exp(f.logsigmoid(rate[a:b, : heads * dk].to(m) + dt_bias.to(m)) * rate_scale).reshape(n, heads, dk)
+                u_scale = torch.ones(n, heads, dtype=m, device=q.device)
             else:
                 qq = qq / torch.sqrt((qq * qq).sum(-1, keepdim=True) + 1e-6) * q_scale
                 kk = kk / torch.sqrt((kk * kk).sum(-1, keepdim=True) + 1e-6)
@@ -433,7 +473,7 @@ class EmuKernels:
 
     def routed_experts(self, h, logits, w_gate_up, w_down, top, out, score="sigmoid", renormalise=False, scale_input=True,
                        activation="clamped_swish", limit=0.0, alpha=1.702, outputs=None, choice_bias=None, renormalise_eps=0.0,
-                       shared=None, shared_gated=False):
+                       shared=None, shared_gated=False, weight_scale=1.0):
         m = self.math
         n_out = logits.shape[1] if outputs is None else outputs
         z = logits[:, :n_out].to(torch.float32)
@@ -445,6 +485,7 @@ class EmuKernels:
         wts = torch.gather(scores, 1, idx)
         if renormalise:
             wts = wts / (wts.sum(-1, keepdim=True) + renormalise_eps)
+        wts = wts * weight_scale
         ff = w_down.shape[2]
         n_real = w_down.shape[0]
         total = torch.zeros((h.shape[0], w_down.shape[1]), dtype=m, device=h.device)

@@ -11,7 +11,7 @@ of three: the way the reference's own benchmark times its generate()); ``prefill
 compares the decode step with the bytes it has to read (every weight once, and the cache of the live requests).
 The weights (2.47 GB) are larger than the L2 cache, so no flush is needed between steps.
 
-``--design rogisun`` (or ``bapavik``, ``lilunex``) is another measurement altogether and leaves the line above as it is: prefill and decode
+``--design rogisun`` (or ``bapavik``, ``lilunex``, ``gebilorn``) is another measurement altogether and leaves the line above as it is: prefill and decode
 throughput of the Rogisun decoder (three layers, one of each mixer, routed experts) at layer sizes of real models,
 beside a Llama decoder of equal width, depth and active feed-forward size, each with the device time of every kernel
 of one prompt step and one decoding step; it prints its own JSON line (see design_bench).
@@ -384,7 +384,30 @@ def lilunex_at(width: int, vocab: int = 32000):
                              "layers": layers, "max_position": CONTEXT})
 
 
-DESIGNS = {"rogisun": rogisun_at, "bapavik": bapavik_at, "lilunex": lilunex_at}
+def gebilorn_at(width: int, vocab: int = 32000):
+    """A Gebilorn configuration with layers of a real model's sizes: attention (heads of 128, half of a head rotated, a window of
+    1,024 keys that keeps the first four, a sink, an element-wise gate) with experts and a gated shared expert; a parallel pair
+    (convolved window attention with heads of 128 beside a decaying matrix state per head of 128 x 128) with a dense gelu-gated
+    feed-forward; latent attention (cached rows of 192 + 64, heads of 128 + 64, a query latent of 3/8 of the width) with experts."""
+    from serve_b200.config import config_from_dict
+
+    heads, experts, top, ff = DESIGN_SIZES[str(width)]
+    moe = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top, "scale": 1.5}, "shared": {"ff": ff}}
+    att = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 0.08, "mask": {"size": 1024, "keep_first": 4},
+           "rot": {"base": 500000.0, "dims": 64, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+    par = {"left": {"heads": heads // 2, "kv_heads": max(1, heads // 8), "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "conv": 4,
+                    "mask": {"size": 1024}},
+           "right": {"heads": heads // 2, "dim": 128, "vdim": 128, "tau": 16.0, "rank": 64}, "left_scale": 0.8, "right_scale": 0.5}
+    lat = {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 192, "q_rank": 3 * width // 8, "scale": 192 ** -0.5,
+           "rot": {"base": 10000.0, "dims": 64}}
+    layers = [{"type": "attention", "mixer": att, "mlp": moe}, {"type": "parallel", "mixer": par, "mlp": {"kind": "dense", "ff": top * ff}},
+              {"type": "latent_attention", "mixer": lat, "mlp": moe}]
+    return config_from_dict({"architecture": "Gebilorn", "width": width, "vocab": vocab, "norm": {"eps": 1e-5}, "logit_softcap": 30.0,
+                             "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 32003, "mul_cur": 17}}, "layers": layers,
+                             "max_position": CONTEXT})
+
+
+DESIGNS = {"rogisun": rogisun_at, "bapavik": bapavik_at, "lilunex": lilunex_at, "gebilorn": gebilorn_at}
 
 
 def kernel_times(eng, entries, end):
@@ -431,7 +454,7 @@ def prefill_many(eng, vocab, requests, each, reps=5, seed=11):
 
 def design_bench(args):
     """Prefill (one prompt of 2,048 tokens) and decode (batch 8 after 2,048-token prompts, from CUDA graphs) of the named design
-    (Rogisun, Bapavik or Lilunex) and of the Llama decoder of equal size, at each width asked for, bfloat16, random weights; CUDA events on the stream, the
+    (Rogisun, Bapavik, Lilunex or Gebilorn) and of the Llama decoder of equal size, at each width asked for, bfloat16, random weights; CUDA events on the stream, the
     weights alone exceed the L2 cache. Prints one JSON line: per width and design the two rates, the rate of a step of 8 prompts
     of 256 tokens (the same tokens side by side: what a recurrence walks in turn for one prompt it walks at once for eight),
     and the kernels of one prompt step and one (eager) decoding step with their device times."""

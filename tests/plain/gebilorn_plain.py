@@ -188,7 +188,7 @@ def chosen_experts(h, w, p, f):
     s = torch.softmax(h @ w[p + "router"].T, -1)
     top = f["router"]["top"]
     idx = torch.sort(s, dim=-1, descending=True, stable=True).indices[:, :top]
-    return idx, torch.gather(s, 1, idx) * f["router"]["scale"]
+    return idx, torch.gather(s, 1, idx) * (f["router"].get("scale") or 1.0)
 
 
 def expert_ff(h, w, p, f):
@@ -210,8 +210,8 @@ def feed_forward(h, w, p, f):
 
 # ---- the model ------------------------------------------------------------------------------------------------
 def embed(tokens, w, cfg):
-    x = w["embed"][tokens] * cfg["embedding"]["scale"]
-    b = (cfg["embedding"] or {}).get("bigram")
+    x = w["embed"][tokens] * (cfg.get("embedding") or {}).get("scale", 1.0)
+    b = (cfg.get("embedding") or {}).get("bigram")
     if b:
         rows = [b["buckets"]] + [(tokens[i - 1] * b["mul_prev"] + tokens[i] * b["mul_cur"]) % b["buckets"] for i in range(1, len(tokens))]
         x = x + w["bigram"][torch.tensor(rows)]

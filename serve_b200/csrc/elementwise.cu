@@ -62,23 +62,25 @@ SB_EXPORT int sb_embedding(const int* tokens, const void* table, float* out, int
 }
 
 // ---------------------------------------------------------- add + RMSNorm
-// One block per row. x (float residual) += delta if given (and is written back
+// One block per row. x (float residual) += delta (+ delta2) if given (and is written back
 // when update_x); out = x * rsqrt(mean(x^2) + eps) * weight, rounded once.
 // With rows != nullptr, row b of the output comes from x[rows[b]] and x is not
 // written.
 template <typename T, typename W>
-__global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta, const int* __restrict__ rows,
-                                   const W* __restrict__ weight, T* __restrict__ out, int dim, float eps) {
+__global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta, const T* __restrict__ delta2,
+                                   const int* __restrict__ rows, const W* __restrict__ weight, T* __restrict__ out, int dim, float eps) {
   __shared__ float red[32];
   extern __shared__ float rowbuf[];  // dim floats
   const int b = blockIdx.x;
   const int src_row = rows ? rows[b] : b;
   float* xr = x + (size_t)src_row * dim;
   const T* dr = delta ? delta + (size_t)src_row * dim : nullptr;
+  const T* dr2 = delta2 ? delta2 + (size_t)src_row * dim : nullptr;
   float ss = 0.f;
   for (int i = threadIdx.x; i < dim; i += blockDim.x) {
     float v = xr[i];
     if (dr) v += to_float(dr[i]);
+    if (dr2) v += to_float(dr2[i]);
     rowbuf[i] = v;
     ss += v * v;
   }
@@ -115,13 +117,14 @@ template <> struct Vec4<__nv_bfloat16> {
 };
 
 template <typename T, typename W, int VPT>
-__global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const T* __restrict__ delta, const int* __restrict__ rows,
-                                       const W* __restrict__ weight, T* __restrict__ out, int dim, float eps) {
+__global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const T* __restrict__ delta, const T* __restrict__ delta2,
+                                       const int* __restrict__ rows, const W* __restrict__ weight, T* __restrict__ out, int dim, float eps) {
   __shared__ float red[32];
   const int b = blockIdx.x;
   const int src_row = rows ? rows[b] : b;
   float* xr = x + (size_t)src_row * dim;
   const T* dr = delta ? delta + (size_t)src_row * dim : nullptr;
+  const T* dr2 = delta2 ? delta2 + (size_t)src_row * dim : nullptr;
   const int nvec = dim >> 2;
   float4 v[VPT], wv[VPT];
   float ss = 0.f;
@@ -139,6 +142,10 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const T* __restric
       v[k] = Vec4<float>::load(xr + i * 4);
       if (dr) {
         const float4 d = Vec4<T>::load(dr + i * 4);
+        v[k].x += d.x; v[k].y += d.y; v[k].z += d.z; v[k].w += d.w;
+      }
+      if (dr2) {
+        const float4 d = Vec4<T>::load(dr2 + i * 4);
         v[k].x += d.x; v[k].y += d.y; v[k].z += d.z; v[k].w += d.w;
       }
     }
@@ -164,9 +171,9 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ x, const T* __restric
 }
 
 template <typename T>
-static int launch_add_rmsnorm(float* x, const void* delta, const int* rows, const void* weight, int weight_dtype, void* out,
-                              int n_rows, int dim, float eps, cudaStream_t stream) {
-  if ((dim % 4) == 0 && aligned16(x) && aligned16(out) && aligned16(weight) && (!delta || aligned16(delta))) {
+static int launch_add_rmsnorm(float* x, const void* delta, const void* delta2, const int* rows, const void* weight, int weight_dtype,
+                              void* out, int n_rows, int dim, float eps, cudaStream_t stream) {
+  if ((dim % 4) == 0 && aligned16(x) && aligned16(out) && aligned16(weight) && (!delta || aligned16(delta)) && (!delta2 || aligned16(delta2))) {
     // vector path: threads so that each holds at most 2 (or 8) float4
     const int nvec = dim / 4;
     int threads = nvec <= 128 ? 128 : (nvec <= 256 ? 256 : 512);
@@ -184,10 +191,10 @@ static int launch_add_rmsnorm(float* x, const void* delta, const int* rows, cons
   do {                                                                                                                    \
     if (ahead) {                                                                                                          \
       SB_PDL_CHECK(launch_pdl(add_rmsnorm_vec_kernel<T, WT, VPT>, dim3(n_rows), dim3(threads), 0, stream, x,              \
-                              (const T*)delta, rows, (const WT*)weight, (T*)out, dim, eps));                              \
+                              (const T*)delta, (const T*)delta2, rows, (const WT*)weight, (T*)out, dim, eps));            \
     } else {                                                                                                              \
-      add_rmsnorm_vec_kernel<T, WT, VPT><<<n_rows, threads, 0, stream>>>(x, (const T*)delta, rows, (const WT*)weight,     \
-                                                                         (T*)out, dim, eps);                              \
+      add_rmsnorm_vec_kernel<T, WT, VPT><<<n_rows, threads, 0, stream>>>(x, (const T*)delta, (const T*)delta2, rows,      \
+                                                                         (const WT*)weight, (T*)out, dim, eps);           \
     }                                                                                                                     \
   } while (0)
       if (weight_dtype == SB_DTYPE_F32) {
@@ -207,11 +214,11 @@ static int launch_add_rmsnorm(float* x, const void* delta, const int* rows, cons
   if (weight_dtype == SB_DTYPE_F32) {
     auto k = add_rmsnorm_kernel<T, float>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    k<<<n_rows, threads, smem, stream>>>(x, (const T*)delta, rows, (const float*)weight, (T*)out, dim, eps);
+    k<<<n_rows, threads, smem, stream>>>(x, (const T*)delta, (const T*)delta2, rows, (const float*)weight, (T*)out, dim, eps);
   } else if (weight_dtype == SB_DTYPE_BF16) {
     auto k = add_rmsnorm_kernel<T, __nv_bfloat16>;
     if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    k<<<n_rows, threads, smem, stream>>>(x, (const T*)delta, rows, (const __nv_bfloat16*)weight, (T*)out, dim, eps);
+    k<<<n_rows, threads, smem, stream>>>(x, (const T*)delta, (const T*)delta2, rows, (const __nv_bfloat16*)weight, (T*)out, dim, eps);
   } else {
     return SB_ERR_DTYPE;
   }
@@ -223,9 +230,20 @@ SB_EXPORT int sb_add_rmsnorm(float* x, const void* delta, const int* rows, const
                              int n_rows, int dim, float eps, int dtype, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (dim <= 0) return SB_ERR_SHAPE;
-  if (dtype == SB_DTYPE_F32) return launch_add_rmsnorm<float>(x, delta, rows, weight, weight_dtype, out, n_rows, dim, eps, stream);
+  if (dtype == SB_DTYPE_F32) return launch_add_rmsnorm<float>(x, delta, nullptr, rows, weight, weight_dtype, out, n_rows, dim, eps, stream);
   if (dtype == SB_DTYPE_BF16)
-    return launch_add_rmsnorm<__nv_bfloat16>(x, delta, rows, weight, weight_dtype, out, n_rows, dim, eps, stream);
+    return launch_add_rmsnorm<__nv_bfloat16>(x, delta, nullptr, rows, weight, weight_dtype, out, n_rows, dim, eps, stream);
+  return SB_ERR_DTYPE;
+}
+
+// As sb_add_rmsnorm with two deltas (the outputs of two sub-layers that read the same norm): x += delta + delta2, each added in float.
+SB_EXPORT int sb_add2_rmsnorm(float* x, const void* delta, const void* delta2, const int* rows, const void* weight, int weight_dtype,
+                              void* out, int n_rows, int dim, float eps, int dtype, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (dim <= 0 || !delta || !delta2) return SB_ERR_SHAPE;
+  if (dtype == SB_DTYPE_F32) return launch_add_rmsnorm<float>(x, delta, delta2, rows, weight, weight_dtype, out, n_rows, dim, eps, stream);
+  if (dtype == SB_DTYPE_BF16)
+    return launch_add_rmsnorm<__nv_bfloat16>(x, delta, delta2, rows, weight, weight_dtype, out, n_rows, dim, eps, stream);
   return SB_ERR_DTYPE;
 }
 

@@ -113,7 +113,7 @@ struct RopeEpilogue {
   bf16* vc;
   int* errors;
   int rot, H, Hkv, D, bt_width, ps, num_pages, write_cache;
-  // gate/up epilogue: limit > 0 asks for the clamped activation g <- min(g, limit), u <- clamp(u, -limit, limit),
+  // gate/up epilogue: limit < 0 asks for gelu(g) * u; limit > 0 for the clamped activation g <- min(g, limit), u <- clamp(u, -limit, limit),
   // g * sigmoid(alpha g) * (u + 1) in place of silu(g) * u
   float act_limit, act_alpha;
   // plain products: an activation on every output, after its rounding to bfloat16 (0: none, 1: relu squared, 2: gelu in
@@ -134,6 +134,7 @@ __device__ __forceinline__ float gated_act(float g, float u, float limit, float 
     u = fminf(fmaxf(u, -limit), limit);
     return g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
   }
+  if (limit < 0.f) return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;      // gelu (tanh form) as the gate
   return g / (1.0f + expf(-g)) * u;
 }
 
@@ -724,6 +725,13 @@ SB_EXPORT int sb_gemm_tcgen05_gate_up_clamped(const void* a, const void* w, void
   if (!(limit > 0.f)) return SB_ERR_SHAPE;
   RopeEpilogue ra{};
   ra.act_limit = limit; ra.act_alpha = alpha;
+  return run_product(a, w, out, M, N, K, EPI_GATE_UP, ra, error, stream);
+}
+
+// The gate/up product with gelu(g) * u (the tanh form of gelu) in its epilogue: w [2N, K], out [M, N].
+SB_EXPORT int sb_gemm_tcgen05_gate_up_gelu(const void* a, const void* w, void* out, int M, int N, int K, int* error, cudaStream_t stream) {
+  RopeEpilogue ra{};
+  ra.act_limit = -1.f; ra.act_alpha = 1.f;
   return run_product(a, w, out, M, N, K, EPI_GATE_UP, ra, error, stream);
 }
 

@@ -789,17 +789,12 @@ SB_EXPORT int sb_softcap(float* x, long long total, float cap, cudaStream_t stre
   return 0;
 }
 
-// ------------------------------------------------------------------------------------- residual addition, sigmoid gate
+// ------------------------------------------------------------------------------------- sigmoid gate
 namespace {
 
-template <typename T>
-__global__ void __launch_bounds__(256) residual_add_kernel(float* __restrict__ x, const T* __restrict__ d, size_t total) {
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) x[i] += to_float(d[i]);
-}
-
 // out[t, c] = scale * a[t, c] * sigmoid(gate[t, c / per_gate]) (gate null: scale * a), the product in float, rounded once.
-template <typename T>
-__global__ void __launch_bounds__(256) sigmoid_gate_kernel(const T* __restrict__ a, int a_stride, const T* __restrict__ gate, int gate_stride,
+template <typename T, typename TG>
+__global__ void __launch_bounds__(256) sigmoid_gate_kernel(const T* __restrict__ a, int a_stride, const TG* __restrict__ gate, int gate_stride,
                                                            int per_gate, T* __restrict__ out, int out_stride, int cols, size_t total,
                                                            float scale) {
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
@@ -813,32 +808,25 @@ __global__ void __launch_bounds__(256) sigmoid_gate_kernel(const T* __restrict__
 
 }  // namespace
 
-// x (float, contiguous) += d (contiguous, of ``dtype``).
-SB_EXPORT int sb_residual_add(float* x, const void* d, long long total, int dtype, cudaStream_t stream) {
-  if (total <= 0) return 0;
-  const size_t want = ((size_t)total + 255) / 256;
-  const int blocks = (int)(want < (size_t)sm_count() * 16 ? want : (size_t)sm_count() * 16);
-  if (dtype == SB_DTYPE_F32) residual_add_kernel<float><<<blocks, 256, 0, stream>>>(x, (const float*)d, (size_t)total);
-  else if (dtype == SB_DTYPE_BF16) residual_add_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(x, (const __nv_bfloat16*)d, (size_t)total);
-  else return SB_ERR_DTYPE;
-  SB_LAUNCH_CHECK();
-  return 0;
-}
-
-// a, out [n_rows, cols] (row strides given; may be the same buffer), gate [n_rows, gate_cols] or null; gate_cols divides cols.
+// a, out [n_rows, cols] (row strides given; may be the same buffer), gate [n_rows, gate_cols] or null, of the operands' type or
+// (gate_f32) float; gate_cols divides cols.
 SB_EXPORT int sb_sigmoid_gate(const void* a, int a_stride, const void* gate, int gate_stride, int gate_cols, void* out, int out_stride,
-                              int n_rows, int cols, float scale, int dtype, cudaStream_t stream) {
+                              int n_rows, int cols, float scale, int dtype, int gate_f32, cudaStream_t stream) {
   if (n_rows <= 0 || cols <= 0) return 0;
   if (a_stride < cols || out_stride < cols || (gate && (gate_cols <= 0 || cols % gate_cols || gate_stride < gate_cols))) return SB_ERR_SHAPE;
   const int per_gate = gate ? cols / gate_cols : 1;
   const size_t total = (size_t)n_rows * cols, want = (total + 255) / 256;
   const int blocks = (int)(want < (size_t)sm_count() * 16 ? want : (size_t)sm_count() * 16);
   if (dtype == SB_DTYPE_F32)
-    sigmoid_gate_kernel<float><<<blocks, 256, 0, stream>>>((const float*)a, a_stride, (const float*)gate, gate_stride, per_gate, (float*)out,
-                                                           out_stride, cols, total, scale);
+    sigmoid_gate_kernel<float, float><<<blocks, 256, 0, stream>>>((const float*)a, a_stride, (const float*)gate, gate_stride, per_gate,
+                                                                  (float*)out, out_stride, cols, total, scale);
+  else if (dtype == SB_DTYPE_BF16 && gate_f32)
+    sigmoid_gate_kernel<__nv_bfloat16, float><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)a, a_stride, (const float*)gate, gate_stride,
+                                                                          per_gate, (__nv_bfloat16*)out, out_stride, cols, total, scale);
   else if (dtype == SB_DTYPE_BF16)
-    sigmoid_gate_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)a, a_stride, (const __nv_bfloat16*)gate, gate_stride,
-                                                                   per_gate, (__nv_bfloat16*)out, out_stride, cols, total, scale);
+    sigmoid_gate_kernel<__nv_bfloat16, __nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)a, a_stride, (const __nv_bfloat16*)gate,
+                                                                                  gate_stride, per_gate, (__nv_bfloat16*)out, out_stride, cols,
+                                                                                  total, scale);
   else return SB_ERR_DTYPE;
   SB_LAUNCH_CHECK();
   return 0;

@@ -51,7 +51,7 @@ struct RopeArgs {
   int bt_width, ps, num_pages, write_cache;
   int* errors;
   int late_trigger;    // let the kernel after this one start only when this kernel's products are done (see launch_mt)
-  // gate/up products: limit > 0 asks for the clamped activation g <- min(g, limit), u <- clamp(u, -limit, limit),
+  // gate/up products: limit < 0 asks for gelu(g) * u; limit > 0 for the clamped activation g <- min(g, limit), u <- clamp(u, -limit, limit),
   // g * sigmoid(alpha g) * (u + 1) in place of silu(g) * u
   float act_limit, act_alpha;
   // plain products: an activation on every output, after its rounding to the output type (0: none, 1: relu squared,
@@ -197,6 +197,8 @@ __global__ void __launch_bounds__(THREADS, 2) skinny_linear_kernel(const bf16* _
       if (ra.act_limit > 0.f) {
         const float gc = fminf(gte, ra.act_limit), uc = fminf(fmaxf(up, -ra.act_limit), ra.act_limit);
         v = gc / (1.0f + expf(-ra.act_alpha * gc)) * (uc + 1.0f);
+      } else if (ra.act_limit < 0.f) {
+        v = 0.5f * gte * (1.f + tanhf(0.7978845608028654f * (gte + 0.044715f * gte * gte * gte))) * up;      // gelu (tanh form) as the gate
       } else {
         v = gte / (1.0f + expf(-gte)) * up;
       }
@@ -390,6 +392,13 @@ SB_EXPORT int sb_skinny_linear_supports(int M, int N, int K, int gate_up) {
   (void)gate_up;
   if (M < 1 || M > 16 || N < 1 || K < 32 || (K % 32)) return 0;
   return 1;
+}
+
+// The gate/up product with gelu(g) * u (the tanh form of gelu) in its epilogue: w [2N, K], out [M, N] bf16.
+SB_EXPORT int sb_skinny_gate_up_gelu(const void* a, const void* w, void* out, int M, int N, int K, cudaStream_t stream) {
+  if (!sb_skinny_linear_supports(M, N, K, 1)) return SB_ERR_SHAPE;
+  if (!aligned16(a) || !aligned16(w)) return SB_ERR_ALIGN;
+  return launch_mt<true, bf16>(a, w, out, M, N, K, stream, -1.f, 1.f);
 }
 
 // The gate/up product with the clamped activation in its epilogue (see RopeArgs): w [2N, K], out [M, N] bf16.

@@ -295,22 +295,17 @@ class CudaKernels:
         _check(self._prep_lib().sb_bias_round(_p(sums), sums.stride(0), _p(bias), _p(out), out.stride(0), sums.shape[0], sums.shape[1],
                                               _DT[out.dtype], self._s()), "bias")
 
-    def residual_add(self, x, delta) -> None:
-        """x (float residual stream, contiguous) += delta (activations or float, contiguous)."""
-        if x.dtype != torch.float32 or x.shape != delta.shape or not x.is_contiguous() or not delta.is_contiguous():
-            raise KernelError("residual_add: a float stream and a delta of its shape")
-        self.launches += 1
-        _check(self._prep_lib().sb_residual_add(_p(x), _p(delta), ctypes.c_longlong(x.numel()), _DT[delta.dtype], self._s()), "residual addition")
-
     def sigmoid_gate(self, a, gate, out, scale: float = 1.0) -> None:
-        """out = scale * a * sigmoid(gate): gate [T, g] with g dividing a's columns (one number for each run of columns), or None.
-        a and out may be column slices, and the same buffer."""
-        if a.shape != out.shape or a.dtype != out.dtype or a.stride(1) != 1 or out.stride(1) != 1 or (gate is not None and (gate.dtype != a.dtype or gate.stride(1) != 1)):
-            raise KernelError("sigmoid_gate: operands of one type, contiguous along their rows")
+        """out = scale * a * sigmoid(gate): gate [T, g] with g dividing a's columns (one number for each run of columns), of a's type
+        or float, or None. a, gate and out may be column slices, a and out the same buffer."""
+        if a.shape != out.shape or a.dtype != out.dtype or a.stride(1) != 1 or out.stride(1) != 1 or (
+                gate is not None and (gate.dtype not in (a.dtype, torch.float32) or gate.stride(1) != 1)):
+            raise KernelError("sigmoid_gate: operands of one type (the gate may be float), contiguous along their rows")
         self.launches += 1
         _check(self._prep_lib().sb_sigmoid_gate(_p(a), a.stride(0), _p(gate), gate.stride(0) if gate is not None else 0,
                                                 gate.shape[1] if gate is not None else 0, _p(out), out.stride(0), a.shape[0], a.shape[1],
-                                                ctypes.c_float(scale), _DT[a.dtype], self._s()), "sigmoid gate")
+                                                ctypes.c_float(scale), _DT[a.dtype], 1 if gate is not None and gate.dtype == torch.float32 else 0,
+                                                self._s()), "sigmoid gate")
 
     def softcap(self, x, cap: float) -> None:
         """x (float, contiguous) <- cap * tanh(x / cap)."""
@@ -323,6 +318,13 @@ class CudaKernels:
         self.launches += 1
         _check(self._core.sb_add_rmsnorm(_p(x), _p(delta), _p(None), _p(weight), _DT[weight.dtype], _p(out), x.shape[0],
                                          x.shape[1], ctypes.c_float(eps), _DT[out.dtype], self._s()), "add_rmsnorm")
+
+    def add2_rmsnorm(self, x, delta, delta2, rows, weight, eps, out) -> None:
+        """As add_rmsnorm (``rows`` None) or add_rmsnorm_rows with two deltas: x += delta + delta2, each added in float."""
+        self.launches += 1
+        n = rows.shape[0] if rows is not None else x.shape[0]
+        _check(self._core.sb_add2_rmsnorm(_p(x), _p(delta), _p(delta2), _p(rows), _p(weight), _DT[weight.dtype], _p(out), n, x.shape[1],
+                                          ctypes.c_float(eps), _DT[out.dtype], self._s()), "add_rmsnorm with two deltas")
 
     def add_rmsnorm_rows(self, x, delta, rows, weight, eps, out) -> None:
         self.launches += 1
@@ -438,6 +440,16 @@ class CudaKernels:
                 _check(self._core.sb_gemm_tcgen05_gate_up_clamped(_p(h), _p(w_gate_up), _p(out), t, inter, k, ctypes.c_float(limit),
                                                                   ctypes.c_float(alpha), self._wait_flag(), self._s()),
                        "tcgen05 gate/up, clamped")
+                return
+        if h.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and activation == "gelu_tanh":
+            if self.use_skinny_linear and self._core.sb_skinny_linear_supports(t, inter, k, 1):
+                self.launches += 1
+                _check(self._core.sb_skinny_gate_up_gelu(_p(h), _p(w_gate_up), _p(out), t, inter, k, self._s()), "skinny gate/up, gelu")
+                return
+            if self._tcgen05_worthwhile(t, 2 * inter) and self._core.sb_gemm_tcgen05_supports(t, inter, k, 1):
+                self.launches += 1
+                _check(self._core.sb_gemm_tcgen05_gate_up_gelu(_p(h), _p(w_gate_up), _p(out), t, inter, k, self._wait_flag(), self._s()),
+                       "tcgen05 gate/up, gelu")
                 return
         gate_up = torch.empty((t, 2 * inter), dtype=h.dtype, device=h.device)
         self.linear(h, w_gate_up, gate_up)

@@ -1,6 +1,6 @@
 """Parts a layer is put together from; importing this package registers the built-in ones."""
 from .base import (  # noqa: F401
-    Block, CacheNeed, DeferredNorm, FeedForward, Mixer, Norm, Part, PositionEncoding, SequenceFilter, TensorDecl,
+    Block, CacheNeed, DeferredNorm, DeltaPair, FeedForward, Mixer, Norm, Part, PositionEncoding, SequenceFilter, TensorDecl,
     build_part, plain_delta, register_part, registered,
 )
 from . import norm, rotary, attention, feed_forward, block, embedding  # noqa: F401

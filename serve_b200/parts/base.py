@@ -168,9 +168,20 @@ class DeferredNorm:
         return self.norm.apply(self.a)
 
 
+class DeltaPair:
+    """The outputs of two sub-layers that read the same norm and both still have to join the residual stream. A norm that
+    can add both in its own kernel takes the pair as it is; any other asks for ``plain()``, their float sum."""
+
+    def __init__(self, a, b):
+        self.a, self.b = a, b
+
+    def plain(self):
+        return self.a.float() + self.b.float()
+
+
 def plain_delta(delta):
     """A pending delta as a tensor (or None), whatever form it was handed on in."""
-    return delta.plain() if isinstance(delta, DeferredNorm) else delta
+    return delta.plain() if isinstance(delta, (DeferredNorm, DeltaPair)) else delta
 
 
 class Norm(Part):

@@ -7,7 +7,7 @@ inside the next norm kernel.
 """
 from __future__ import annotations
 
-from .base import Block, CacheNeed, DeferredNorm, register_part
+from .base import Block, CacheNeed, DeferredNorm, DeltaPair, register_part
 
 
 @register_part("block", "pre_norm")
@@ -94,8 +94,8 @@ class SandwichNormBlock(Block):
 @register_part("block", "parallel_residual")
 class ParallelResidualBlock(Block):
     """One norm whose output both sub-layers read: h = norm(x); x = x + (mixer(h) + ffn(h)). The feed-forward may be left
-    out. The mixer's output joins the float residual stream at once and the feed-forward's travels as the pending delta, so
-    both additions are float."""
+    out. Both outputs travel as the pending delta (a ``DeltaPair``); the norm that reads the residual stream next adds each
+    of them in float in its own kernel, or, if it cannot, gets their float sum."""
 
     wants = {"norm": "norm", "mixer": "mixer", "feed_forward": "feed_forward"}
     optional = ("feed_forward",)
@@ -105,6 +105,4 @@ class ParallelResidualBlock(Block):
         a = self.mixer.forward(h, ctx, cache)
         if self.feed_forward is None:
             return x, a
-        f = self.feed_forward.forward(h, ctx)
-        self.rt.kernels.residual_add(x, a)
-        return x, f
+        return x, DeltaPair(a, self.feed_forward.forward(h, ctx))

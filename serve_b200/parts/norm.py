@@ -8,7 +8,7 @@ weight is taken in float32 before the single rounding to the activation dtype.
 """
 from __future__ import annotations
 
-from .base import DeferredNorm, Norm, TensorDecl, plain_delta, register_part
+from .base import DeferredNorm, DeltaPair, Norm, TensorDecl, plain_delta, register_part
 
 
 @register_part("norm", "rms")
@@ -38,11 +38,17 @@ class RMSNorm(Norm):
 
     def forward(self, x, delta, ctx):
         out = self.rt.empty_act((x.shape[0], self.size))
+        if isinstance(delta, DeltaPair) and delta.a.dtype == out.dtype and delta.b.dtype == out.dtype:
+            self.rt.kernels.add2_rmsnorm(x, delta.a, delta.b, None, self.weight, self.eps, out)      # both join in this kernel, in float
+            return out
         self.rt.kernels.add_rmsnorm(x, plain_delta(delta), self.weight, self.eps, out)
         return out
 
     def forward_rows(self, x, delta, rows, ctx):
         out = self.rt.empty_act((rows.shape[0], self.size))
+        if isinstance(delta, DeltaPair) and delta.a.dtype == out.dtype and delta.b.dtype == out.dtype:
+            self.rt.kernels.add2_rmsnorm(x, delta.a, delta.b, rows, self.weight, self.eps, out)
+            return out
         self.rt.kernels.add_rmsnorm_rows(x, plain_delta(delta), rows, self.weight, self.eps, out)
         return out
 
@@ -55,14 +61,18 @@ class LayerNorm(RMSNorm):
     def fused_description(self):
         return None     # the kernel that runs whole layers knows RMS norms only
 
+    def _delta(self, delta):
+        d = plain_delta(delta)
+        return d.to(self.rt.act_dtype) if isinstance(delta, DeltaPair) else d        # (this kernel reads a delta of the activations' type)
+
     def forward(self, x, delta, ctx):
         out = self.rt.empty_act((x.shape[0], self.size))
-        self.rt.kernels.add_layernorm(x, plain_delta(delta), self.weight, self.eps, out)
+        self.rt.kernels.add_layernorm(x, self._delta(delta), self.weight, self.eps, out)
         return out
 
     def forward_rows(self, x, delta, rows, ctx):
         out = self.rt.empty_act((rows.shape[0], self.size))
-        self.rt.kernels.add_layernorm_rows(x, plain_delta(delta), rows, self.weight, self.eps, out)
+        self.rt.kernels.add_layernorm_rows(x, self._delta(delta), rows, self.weight, self.eps, out)
         return out
 
 
@@ -101,7 +111,7 @@ class DynamicTanh(Norm):
             if isinstance(delta.norm, DynamicTanh):
                 return delta.a, delta.norm.params
             return delta.plain(), None
-        return delta, None
+        return plain_delta(delta), None
 
     def forward(self, x, delta, ctx):
         out = self.rt.empty_act((x.shape[0], self.size))

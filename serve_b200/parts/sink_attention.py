@@ -107,7 +107,13 @@ class RotarySinkAttention(Mixer):
     def load(self, tensors):
         d = self.head_dim
         shapes = [("q", self.heads, self.dim)] + ([("k", self.kv_heads, self.dim), ("v", self.kv_heads, self.vdim)] if self.own_kv else [])
-        self.w_in = torch.cat([_pad_heads(tensors[self._name(n)], h, size, d) for n, h, size in shapes], dim=0).contiguous()
+        rows = [_pad_heads(tensors[self._name(n)], h, size, d) for n, h, size in shapes]
+        # the gate's projection rides along as more rows of the same product: its float sums are the gate
+        if self.gate == "element":
+            rows.append(_pad_heads(tensors[self._name("g")], self.heads, self.vdim, d))
+        elif self.gate == "head":
+            rows.append(_pad_heads(tensors[self._name("g")], 1, self.heads, self.gate_cols))
+        self.w_in = torch.cat(rows, dim=0).contiguous()
         vec = lambda name, h, size: _pad_heads(tensors[self._name(name)].float().view(-1, 1), h, size, d).view(-1)
         # float vectors laid out like the padded projection: the bias of every column, the norm weight of the query and key columns
         self.b_in = torch.cat([vec(n + ".b", h, size) for n, h, size in shapes]).contiguous() if self.bias else None
@@ -123,11 +129,6 @@ class RotarySinkAttention(Mixer):
         self.w_o = w_o.contiguous()
         self.b_o = tensors[self._name("o.b")].float().contiguous() if self.out_bias else None
         self.sinks = tensors[self._name("sink")].float().contiguous() if self.sink else None
-        self.w_gate = None
-        if self.gate == "element":
-            self.w_gate = _pad_heads(tensors[self._name("g")], self.heads, self.vdim, d).contiguous()
-        elif self.gate == "head":
-            self.w_gate = _pad_heads(tensors[self._name("g")], 1, self.heads, self.gate_cols).contiguous()
         if self.conv is not None:
             # the filters of the padded channels are zero, like the projection's padded rows
             padded = {self._name(n + ".conv"): _pad_heads(tensors[self._name(n + ".conv")], h, size, d) for n, h, size in shapes}
@@ -146,12 +147,12 @@ class RotarySinkAttention(Mixer):
         k = self.rt.kernels
         t, d = h.shape[0], self.head_dim
         n_qkv = (self.heads + 2 * self.cached_heads) * d
-        sums = torch.empty((t, n_qkv), dtype=torch.float32, device=h.device)
+        sums = torch.empty((t, n_qkv + self.gate_cols), dtype=torch.float32, device=h.device)
         k.linear(h, self.w_in, sums)
         table = ctx.block_tables[cache.group]
         if self.conv is not None:
             proj = self.rt.empty_act((t, n_qkv))
-            k.bias_round(sums, self.b_in, proj)
+            k.bias_round(sums[:, :n_qkv], self.b_in, proj)
             q = self.conv.forward(proj, ctx, cache)                        # [T, (H + 2 G) * D]: queries, then keys and values
             k.kv_norm_cache_write(q, ctx.positions, ctx.token_row, self.heads, self.kv_heads, d, 0, 0.0, cache.k, cache.v, table, cache.page_size)
         else:
@@ -167,12 +168,7 @@ class RotarySinkAttention(Mixer):
                     cache.page_size, self.scale, self.window or 0, attn, ctx.shape, sinks=self.sinks,
                     **({"keep_first": self.keep_first} if self.keep_first else {}))
         if not direct:
-            gate = None
-            if self.gate is not None:
-                gate = self.rt.empty_act((t, self.gate_cols))
-                k.linear(h, self.w_gate, gate)
-                if self.gate == "head":
-                    gate = gate[:, : self.heads]
+            gate = None if self.gate is None else sums[:, n_qkv: n_qkv + (self.heads if self.gate == "head" else self.gate_cols)]
             k.sigmoid_gate(attn, gate, out, scale)
 
     def forward(self, h, ctx, cache):

@@ -61,9 +61,6 @@ class EmuKernels:
     def bias_round(self, sums, bias, out):
         out.copy_((sums if bias is None else sums + bias.to(sums.dtype)).to(out.dtype))
 
-    def residual_add(self, x, delta):
-        x.add_(delta.to(x.dtype))
-
     def sigmoid_gate(self, a, gate, out, scale=1.0):
         v = a.to(self.math) * scale
         if gate is not None:
@@ -97,6 +94,14 @@ class EmuKernels:
         if delta is not None:
             x.add_(delta.to(x.dtype))
         out.copy_(self._norm(x, weight, eps).to(out.dtype))
+
+    def add2_rmsnorm(self, x, delta, delta2, rows, weight, eps, out):
+        if rows is None:
+            x.add_(delta.to(x.dtype)).add_(delta2.to(x.dtype))
+            out.copy_(self._norm(x, weight, eps).to(out.dtype))
+        else:
+            v = x[rows.long()] + delta[rows.long()].to(x.dtype) + delta2[rows.long()].to(x.dtype)
+            out.copy_(self._norm(v, weight, eps).to(out.dtype))
 
     def add_rmsnorm_rows(self, x, delta, rows, weight, eps, out):
         v = x[rows.long()]
@@ -222,10 +227,10 @@ class EmuKernels:
     def qk_prepare(self, sums, bias, positions, token_row, heads, kv_heads, head_dim, dim, q_weight, k_weight, eps, inv_freq, rot_dims,
                    q_out, k_cache, v_cache, block_table, page_size, head_norm=False):
         t, d, m = sums.shape[0], head_dim, self.math
-        x = sums.to(m)
+        x = sums[:, : (heads + 2 * kv_heads) * d].to(m)      # (the row may go on with columns that are not the kernel's)
         if bias is not None:
             x = x + bias.to(m)
-        x = x.view(t, heads + 2 * kv_heads, d)
+        x = x.reshape(t, heads + 2 * kv_heads, d)
         ang = positions.to(torch.float32)[:, None] * inv_freq.to(torch.float32)[None, : rot_dims // 2]
         cos, sin = ang.cos().to(m)[:, None, :], ang.sin().to(m)[:, None, :]
 

@@ -253,7 +253,8 @@ ATTS = [ATT(4, 2, 24, 16, 0.2, 20, 3, 10000.0, 16, (4.0, 1.0, 4.0, 32)), ATT(6, 
 PARS = [PAR(4, 2, 24, 16, 0.2, 3, 20, 2, 16, 24, 8.0, 0.7, 0.6), PAR(6, 3, 12, 20, 0.3, 4, 50, 3, 12, 20, 16.0, 0.5, 1.25),
         PAR(3, 1, 16, 8, 0.3, 2, 5, 1, 32, 16, 1.0, 0.9, 0.4), PAR(2, 2, 64, 32, 0.1, 1, 1, 2, 64, 64, 2.5, 1.0, 1.0)]
 LATS = [LAT(4, 16, 8, 24, 40, 28, 0.2, 10000.0), LAT(5, 12, 6, 10, 30, 17, 0.22, 3000.0), LAT(3, 8, 8, 16, 24, 12, 0.25, 100.0),
-        LAT(1, 24, 4, 16, 20, 50, 0.19, 500.0)]
+        LAT(1, 24, 4, 16, 20, 50, 0.19, 500.0),
+        LAT(2, 16, 8, 16, 264, 20, 0.2, 100.0)]      # a latent row wider than the attention kernels take: keys and values cached per head
 WIDTHS = (64, 100, 48, 40, 72, 56)
 
 
@@ -464,13 +465,14 @@ def test_convolved_attention_window_edges(backend, cuts, size):
 
     def tweak(w, p):
         w[p + "left.sink"].fill_(-4.0)
-        for name in ("q", "k"):
-            w[p + f"left.{name}"][:, 0] = 0.0
-            w[p + f"left.{name}"][0::16, 0] = 1.0
+        for name in ("q", "k", "v"):
             w[p + f"left.{name}.conv"][:, :-1] = 0.0       # the current token's tap only, so that the key stays one position
             w[p + f"left.{name}.conv"][:, -1] = 1.0
             w[p + f"left.{name}.b"].zero_()
-        w[p + "left.v"][:, 0] = 2.0
+        for name in ("q", "k"):
+            w[p + f"left.{name}"][:, 0] = 0.0
+            w[p + f"left.{name}"][0::16, 0] = 1.0
+        w[p + "left.v"][:, 0] = 4.0
 
     got, want, _ = _mixer_alone(backend, cfg, cuts, x=x, tweak=tweak, page=64, side="left", loose=2.0)
     if 20 + size < n and size > 1:

@@ -163,7 +163,8 @@ __global__ void __launch_bounds__(256) normed_qk_cache_write_kernel(
 // the cache (one key/value head) and, if asked, into row_out [T, row_stride] (its first rank + rd columns); and for every
 // head columns [q_off, D) of q_lat (rows q_stride apart, heads D apart): the rotated query part, then zeros (columns
 // [0, q_off) are made elsewhere: the product of the plain query part with the keys' read-out matrix when q_off = rank,
-// the plain query part itself when q_off = dim).
+// the plain query part itself when q_off = dim). With ``lat`` the latent vector and the shared key part come from a buffer
+// of their own [T, lat_stride] (its first rank + rd columns) instead of the columns after the queries.
 // Rotation: pairs (2 i, 2 i + 1), or with half_pairs (i, i + rot_dims / 2), i < rot_dims / 2, angle = float(position) *
 // inv_freq[i]; the rest passes unchanged.
 template <typename T>
@@ -171,11 +172,14 @@ __global__ void __launch_bounds__(128) latent_prepare_kernel(
     const T* __restrict__ proj, int stride, int n_q, const int* __restrict__ positions, const int* __restrict__ token_row,
     const float* __restrict__ c_weight, float eps, const float* __restrict__ inv_freq, int rot_dims, int H, int dim, int rd, int rank,
     int D, T* __restrict__ q_lat, int q_stride, int q_off, T* __restrict__ row_out, int row_stride, T* __restrict__ kc,
-    const int* __restrict__ block_table, int bt_width, int ps, int num_pages, int write_cache, int* __restrict__ errors, int half_pairs) {
+    const int* __restrict__ block_table, int bt_width, int ps, int num_pages, int write_cache, int* __restrict__ errors, int half_pairs,
+    const T* __restrict__ lat, int lat_stride) {
   __shared__ float red[32];
   extern __shared__ float cs[];            // [rot_dims / 2][2]: cosine and sine of the token's angles
   const int t = blockIdx.x;
   const T* row = proj + (size_t)t * stride;
+  // the latent vector and the shared key part: columns n_q .. of proj, or a buffer of their own
+  const T* lrow = lat ? lat + (size_t)t * lat_stride : row + n_q;
   const int pos = positions[t];
   const int half = rot_dims / 2;
   for (int i = threadIdx.x; i < half; i += blockDim.x) {
@@ -185,7 +189,7 @@ __global__ void __launch_bounds__(128) latent_prepare_kernel(
     cs[2 * i + 1] = s;
   }
   float ss = 0.f;
-  for (int i = threadIdx.x; i < rank; i += blockDim.x) { const float v = to_float(row[n_q + i]); ss += v * v; }
+  for (int i = threadIdx.x; i < rank; i += blockDim.x) { const float v = to_float(lrow[i]); ss += v * v; }
   ss = block_sum(ss, red);                 // (its barriers also publish cs)
   const float inv = 1.0f / sqrtf(ss / (float)rank + eps);
   // element j of a rotated part whose plain values start at src
@@ -208,7 +212,7 @@ __global__ void __launch_bounds__(128) latent_prepare_kernel(
   }
   if (row_out != nullptr) {
     for (int i = threadIdx.x; i < rank + rd; i += blockDim.x) {
-      const float v = i < rank ? to_float(row[n_q + i]) * inv * c_weight[i] : rotated(row + n_q + rank, i - rank);
+      const float v = i < rank ? to_float(lrow[i]) * inv * c_weight[i] : rotated(lrow + rank, i - rank);
       row_out[(size_t)t * row_stride + i] = from_float<T>(v);
     }
   }
@@ -223,8 +227,8 @@ __global__ void __launch_bounds__(128) latent_prepare_kernel(
   T* dst = kc + ((size_t)page * ps + (pos - blk * ps)) * Dc;
   for (int i = threadIdx.x; i < Dc; i += blockDim.x) {
     float v = 0.f;
-    if (i < rank) v = to_float(row[n_q + i]) * inv * c_weight[i];
-    else if (i < rank + rd) v = rotated(row + n_q + rank, i - rank);
+    if (i < rank) v = to_float(lrow[i]) * inv * c_weight[i];
+    else if (i < rank + rd) v = rotated(lrow + rank, i - rank);
     dst[i] = from_float<T>(v);
   }
 }
@@ -612,10 +616,10 @@ SB_EXPORT int sb_latent_prepare(const void* proj, int stride, int n_q, const int
                                 float eps, const float* inv_freq, int rot_dims, int H, int dim, int rd, int rank, int D, void* q_lat,
                                 int q_stride, int q_off, void* row_out, int row_stride, void* kc, const int* block_table, int bt_width,
                                 int ps, int num_pages, int write_cache, int* errors, int n_tokens, int dtype, int half_pairs,
-                                cudaStream_t stream) {
+                                const void* lat, int lat_stride, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (H <= 0 || dim <= 0 || rd <= 0 || rank <= 0 || rot_dims < 0 || (rot_dims & 1) || rot_dims > rd || q_off < 0 || D < q_off + rd ||
-      q_stride < H * D || n_q != H * (dim + rd) || stride < n_q + rank + rd)
+      q_stride < H * D || n_q != H * (dim + rd) || stride < n_q + (lat ? 0 : rank + rd) || (lat && lat_stride < rank + rd))
     return SB_ERR_SHAPE;
   if (write_cache && D < rank + rd) return SB_ERR_SHAPE;
   if (row_out != nullptr && row_stride < rank + rd) return SB_ERR_SHAPE;
@@ -626,12 +630,12 @@ SB_EXPORT int sb_latent_prepare(const void* proj, int stride, int n_q, const int
     latent_prepare_kernel<float><<<n_tokens, 128, smem, stream>>>((const float*)proj, stride, n_q, positions, token_row, c_weight, eps,
                                                                    inv_freq, rot_dims, H, dim, rd, rank, D, (float*)q_lat, q_stride, q_off,
                                                                    (float*)row_out, row_stride, (float*)kc, block_table, bt_width, ps,
-                                                                   num_pages, write_cache, errors, half_pairs);
+                                                                   num_pages, write_cache, errors, half_pairs, (const float*)lat, lat_stride);
   else if (dtype == SB_DTYPE_BF16)
     latent_prepare_kernel<__nv_bfloat16><<<n_tokens, 128, smem, stream>>>(
         (const __nv_bfloat16*)proj, stride, n_q, positions, token_row, c_weight, eps, inv_freq, rot_dims, H, dim, rd, rank, D,
         (__nv_bfloat16*)q_lat, q_stride, q_off, (__nv_bfloat16*)row_out, row_stride, (__nv_bfloat16*)kc, block_table, bt_width, ps, num_pages,
-        write_cache, errors, half_pairs);
+        write_cache, errors, half_pairs, (const __nv_bfloat16*)lat, lat_stride);
   else
     return SB_ERR_DTYPE;
   SB_LAUNCH_CHECK();

@@ -471,19 +471,21 @@ class CudaKernels:
 
     def latent_prepare(self, proj, n_q, positions, token_row, c_weight, eps, inv_freq, rot_dims, heads, dim, rot_dim, rank, head_dim,
                        q_lat, k_cache, block_table, page_size, write_cache, q_off=None, row_out=None,
-                       half_pairs: bool = False) -> None:
+                       half_pairs: bool = False, latent=None) -> None:
         """Latent attention between its input product and its attention: proj [T, >= n_q + rank + rot_dim] holds the heads'
         queries ([dim | rot_dim] each), the latent vector and the shared key part. Writes the cache row [normed latent | rotated
         key part | zeros] (if write_cache), the same row into row_out [T, >= rank + rot_dim] (if given), and columns
         [q_off, head_dim) of every head of q_lat (rotated query part, zeros); q_off defaults to rank. Rotated pairs are
-        (2 i, 2 i + 1), or with ``half_pairs`` (i, i + rot_dims / 2)."""
+        (2 i, 2 i + 1), or with ``half_pairs`` (i, i + rot_dims / 2). ``latent`` [T, >= rank + rot_dim]: the latent vector and the shared
+        key part in a buffer of their own (proj then holds the queries only)."""
         self.launches += 1
         pages = k_cache.shape[0] if k_cache is not None else 0
         _check(self._prep_lib().sb_latent_prepare(
             _p(proj), proj.stride(0), n_q, _p(positions), _p(token_row), _p(c_weight), ctypes.c_float(eps), _p(inv_freq), rot_dims, heads,
             dim, rot_dim, rank, head_dim, _p(q_lat), q_lat.stride(0), rank if q_off is None else q_off, _p(row_out),
             row_out.stride(0) if row_out is not None else 0, _p(k_cache), _p(block_table), block_table.shape[1], page_size, pages,
-            1 if write_cache else 0, _p(self.errors_tensor()), proj.shape[0], _DT[proj.dtype], 1 if half_pairs else 0, self._s()),
+            1 if write_cache else 0, _p(self.errors_tensor()), proj.shape[0], _DT[proj.dtype], 1 if half_pairs else 0, _p(latent),
+            latent.stride(0) if latent is not None else 0, self._s()),
             "latent attention preparation")
 
     def linear(self, a, w, out) -> None:

@@ -92,9 +92,12 @@ class LatentAttention(Mixer):
         # one product for q and the down projection; its row count is padded to a multiple of 8 (16-byte rows in bfloat16)
         self.n_q = self.heads * (self.dim + self.rot_dim)
         if self.q_rank:
-            # the input's product gives [latent | shared key part | query latent]; the queries' second step fills the columns before
+            # the input's product gives [latent | shared key part | query latent] (rows padded to a multiple of 8); the queries'
+            # second step fills a buffer of its own
             w = torch.cat([tensors[self._name("dkv")], tensors[self._name("dq")]], dim=0)
-            self.n_in = 8 * -(-(self.n_q + w.shape[0]) // 8)
+            self.n_in = 8 * -(-w.shape[0] // 8)
+            if self.n_in != w.shape[0]:
+                w = torch.cat([w, w.new_zeros((self.n_in - w.shape[0], w.shape[1]))], dim=0)
             self.w_uq = tensors[self._name("uq")].contiguous()
             self.q_norm = tensors[self._name("dq.norm")].float().contiguous()
         else:
@@ -136,22 +139,24 @@ class LatentAttention(Mixer):
             raise ValueError("latent_attention writes its heads unscaled")
         k = self.rt.kernels
         t, d = h.shape[0], self.head_dim
-        proj = self.rt.empty_act((t, self.n_in))
+        latent = None
         if self.q_rank:
-            at = self.n_q + self.row
-            k.linear(h, self.w_in, proj[:, self.n_q: at + self.q_rank])
+            latent = self.rt.empty_act((t, self.n_in))
+            k.linear(h, self.w_in, latent)
             cq = self.rt.empty_act((t, self.q_rank))
-            k.gated_norm(proj[:, at: at + self.q_rank], cq, groups=1, eps=self.eps, weight=self.q_norm)
-            k.linear(cq, self.w_uq, proj[:, : self.n_q])
+            k.gated_norm(latent[:, self.row: self.row + self.q_rank], cq, groups=1, eps=self.eps, weight=self.q_norm)
+            proj = self.rt.empty_act((t, self.n_q))
+            k.linear(cq, self.w_uq, proj)
         else:
+            proj = self.rt.empty_act((t, self.n_in))
             k.linear(h, self.w_in, proj)
         table = ctx.block_tables[cache.group]
+        more = {**({"half_pairs": True} if self.half_pairs else {}), **({"latent": latent} if latent is not None else {})}
         if self.per_head:
-            return self._mix_per_head(proj, ctx, cache, table, out)
+            return self._mix_per_head(proj, ctx, cache, table, out, more)
         q_lat = self.rt.empty_act((t, self.heads * d))             # per head [U^T q_plain | q_rot | zeros]
         k.latent_prepare(proj, self.n_q, ctx.positions, ctx.token_row, self.c_norm, self.eps, self.inv_freq, self.rot_dims, self.heads,
-                         self.dim, self.rot_dim, self.rank, d, q_lat, cache.k, table, cache.page_size, cache.writes,
-                         **({"half_pairs": True} if self.half_pairs else {}))
+                         self.dim, self.rot_dim, self.rank, d, q_lat, cache.k, table, cache.page_size, cache.writes, **more)
         q3 = proj[:, : self.n_q].view(t, self.heads, self.dim + self.rot_dim)
         k.linear_batched(q3[:, :, : self.dim], self.w_uk_t, q_lat.view(t, self.heads, d)[:, :, : self.rank])
         o_lat = self.rt.empty_act((t, self.heads * d))
@@ -159,7 +164,7 @@ class LatentAttention(Mixer):
                     cache.page_size, self.scale, self.window or 0, o_lat, ctx.shape)
         k.linear_batched(o_lat.view(t, self.heads, d)[:, :, : self.rank], self.w_uv, out.view(t, self.heads, self.vdim))
 
-    def _mix_per_head(self, proj, ctx, cache, table, out):
+    def _mix_per_head(self, proj, ctx, cache, table, out, more):
         """Keys and values read out per head when the token arrives: qkv [T, 3 H, D] = queries [q_plain | q_rot], keys
         [U_n c | k_rot], values V_n c (zeros after each), cached like any attention's."""
         k = self.rt.kernels
@@ -167,8 +172,7 @@ class LatentAttention(Mixer):
         qkv = torch.zeros((t, 3 * hh * d), dtype=proj.dtype, device=proj.device)
         row = self.rt.empty_act((t, 8 * -(-self.row // 8)))
         k.latent_prepare(proj, self.n_q, ctx.positions, ctx.token_row, self.c_norm, self.eps, self.inv_freq, self.rot_dims, hh, self.dim,
-                         self.rot_dim, self.rank, d, qkv, None, table, cache.page_size, False, q_off=self.dim, row_out=row,
-                         **({"half_pairs": True} if self.half_pairs else {}))
+                         self.rot_dim, self.rank, d, qkv, None, table, cache.page_size, False, q_off=self.dim, row_out=row, **more)
         q3 = qkv.view(t, 3 * hh, d)
         q3[:, :hh, : self.dim].copy_(proj[:, : self.n_q].view(t, hh, self.dim + self.rot_dim)[:, :, : self.dim])
         c = row[:, None, : self.rank].expand(t, hh, self.rank)

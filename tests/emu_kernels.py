@@ -280,7 +280,8 @@ class EmuKernels:
             self._write_pages(v_cache, x[:, heads + kv_heads:], positions, token_row, block_table, page_size)
 
     def latent_prepare(self, proj, n_q, positions, token_row, c_weight, eps, inv_freq, rot_dims, heads, dim, rot_dim, rank, head_dim,
-                       q_lat, k_cache, block_table, page_size, write_cache, q_off=None, row_out=None, half_pairs=False):
+                       q_lat, k_cache, block_table, page_size, write_cache, q_off=None, row_out=None, half_pairs=False,
+                       latent=None):
         t, m = proj.shape[0], self.math
         ang = positions.to(torch.float32)[:, None] * inv_freq.to(torch.float32)[None, :]
         cos, sin = ang.cos().to(m), ang.sin().to(m)
@@ -299,7 +300,7 @@ class EmuKernels:
         ql = q_lat[:, : heads * head_dim].view(t, heads, head_dim)
         ql[:, :, q_off: q_off + rot_dim] = rotate(q[..., dim:]).to(q_lat.dtype)
         ql[:, :, q_off + rot_dim:] = 0
-        down = proj[:, n_q: n_q + rank + rot_dim].to(m)
+        down = (proj[:, n_q: n_q + rank + rot_dim] if latent is None else latent[:, : rank + rot_dim]).to(m)
         c = down[:, :rank]
         c = c * torch.rsqrt(c.pow(2).mean(-1, keepdim=True) + eps) * c_weight.to(m)
         if row_out is not None:

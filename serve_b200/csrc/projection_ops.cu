@@ -732,6 +732,21 @@ __global__ void __launch_bounds__(256) bias_round_kernel(const float* __restrict
   }
 }
 
+// float sums + bias -> bfloat16, four columns a thread.
+__global__ void __launch_bounds__(256) bias_round_vec_kernel(const float* __restrict__ sums, int stride, const float* __restrict__ bias,
+                                                             __nv_bfloat16* __restrict__ out, int out_stride, int cols4, size_t total4) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total4; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = i / cols4;
+    const int c = (int)(i - r * cols4) * 4;
+    float4 v = *reinterpret_cast<const float4*>(sums + r * stride + c);
+    if (bias) {
+      const float4 b = *reinterpret_cast<const float4*>(bias + c);
+      v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+    }
+    store4f<__nv_bfloat16>(out + r * out_stride + c, v);
+  }
+}
+
 __global__ void __launch_bounds__(256) softcap_kernel(float* __restrict__ x, size_t total, float cap, float inv_cap) {
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
     x[i] = cap * tanhf(x[i] * inv_cap);
@@ -772,6 +787,14 @@ SB_EXPORT int sb_bias_round(const float* sums, int stride, const float* bias, vo
                             cudaStream_t stream) {
   if (n_rows <= 0 || cols <= 0) return 0;
   if (stride < cols || out_stride < cols) return SB_ERR_SHAPE;
+  if (dtype == SB_DTYPE_BF16 && cols % 4 == 0 && stride % 4 == 0 && out_stride % 4 == 0 && aligned16(sums) && (!bias || aligned16(bias)) &&
+      (reinterpret_cast<uintptr_t>(out) % 8) == 0) {
+    const size_t total4 = (size_t)n_rows * (cols / 4), want4 = (total4 + 255) / 256;
+    const int blocks4 = (int)(want4 < (size_t)sm_count() * 16 ? want4 : (size_t)sm_count() * 16);
+    bias_round_vec_kernel<<<blocks4, 256, 0, stream>>>(sums, stride, bias, (__nv_bfloat16*)out, out_stride, cols / 4, total4);
+    SB_LAUNCH_CHECK();
+    return 0;
+  }
   const size_t total = (size_t)n_rows * cols, want = (total + 255) / 256;
   const int blocks = (int)(want < (size_t)sm_count() * 16 ? want : (size_t)sm_count() * 16);
   if (dtype == SB_DTYPE_F32) bias_round_kernel<float><<<blocks, 256, 0, stream>>>(sums, stride, bias, (float*)out, out_stride, cols, total);
@@ -810,6 +833,41 @@ __global__ void __launch_bounds__(256) sigmoid_gate_kernel(const T* __restrict__
   }
 }
 
+// The same for bfloat16 operands, eight neighbouring columns a thread (16-byte loads and stores): cols, the row strides and, for a
+// gate per run of columns, the run's length are multiples of 8. PER_ELEMENT: a gate value per column, else one per run.
+template <typename TG, bool PER_ELEMENT>
+__global__ void __launch_bounds__(256) sigmoid_gate_vec_kernel(const __nv_bfloat16* __restrict__ a, int a_stride, const TG* __restrict__ gate,
+                                                               int gate_stride, int per_gate, __nv_bfloat16* __restrict__ out, int out_stride,
+                                                               int cols8, size_t total8, float scale) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total8; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = i / cols8;
+    const int c = (int)(i - r * cols8) * 8;
+    const uint4 av = *reinterpret_cast<const uint4*>(a + r * a_stride + c);
+    const __nv_bfloat16* ae = reinterpret_cast<const __nv_bfloat16*>(&av);
+    float g[8];
+    if (gate == nullptr) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) g[e] = 1.f;
+    } else if (PER_ELEMENT) {
+#pragma unroll
+      for (int e = 0; e < 8; e += 4) {
+        const float4 gv = load4f<TG>(gate + r * gate_stride + c + e);
+        g[e] = 1.f / (1.f + expf(-gv.x)); g[e + 1] = 1.f / (1.f + expf(-gv.y));
+        g[e + 2] = 1.f / (1.f + expf(-gv.z)); g[e + 3] = 1.f / (1.f + expf(-gv.w));
+      }
+    } else {
+      const float one = 1.f / (1.f + expf(-to_float(gate[r * gate_stride + c / per_gate])));
+#pragma unroll
+      for (int e = 0; e < 8; ++e) g[e] = one;
+    }
+    uint4 ov;
+    __nv_bfloat16* oe = reinterpret_cast<__nv_bfloat16*>(&ov);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) oe[e] = __float2bfloat16_rn(to_float(ae[e]) * scale * g[e]);
+    *reinterpret_cast<uint4*>(out + r * out_stride + c) = ov;
+  }
+}
+
 }  // namespace
 
 // a, out [n_rows, cols] (row strides given; may be the same buffer), gate [n_rows, gate_cols] or null, of the operands' type or
@@ -819,6 +877,20 @@ SB_EXPORT int sb_sigmoid_gate(const void* a, int a_stride, const void* gate, int
   if (n_rows <= 0 || cols <= 0) return 0;
   if (a_stride < cols || out_stride < cols || (gate && (gate_cols <= 0 || cols % gate_cols || gate_stride < gate_cols))) return SB_ERR_SHAPE;
   const int per_gate = gate ? cols / gate_cols : 1;
+  if (dtype == SB_DTYPE_BF16 && cols % 8 == 0 && a_stride % 8 == 0 && out_stride % 8 == 0 && aligned16(a) && aligned16(out) &&
+      (!gate || (per_gate == 1 ? (gate_stride % 4 == 0 && (reinterpret_cast<uintptr_t>(gate) % (gate_f32 ? 16 : 8)) == 0) : per_gate % 8 == 0))) {
+    typedef __nv_bfloat16 B;
+    const size_t total8 = (size_t)n_rows * (cols / 8), want8 = (total8 + 255) / 256;
+    const int blocks8 = (int)(want8 < (size_t)sm_count() * 16 ? want8 : (size_t)sm_count() * 16);
+#define SB_GATE_VEC(TG, PE)                                                                                                           \
+  sigmoid_gate_vec_kernel<TG, PE><<<blocks8, 256, 0, stream>>>((const B*)a, a_stride, (const TG*)gate, gate_stride, per_gate, (B*)out, \
+                                                              out_stride, cols / 8, total8, scale)
+    if (gate_f32) { if (per_gate == 1) SB_GATE_VEC(float, true); else SB_GATE_VEC(float, false); }
+    else { if (per_gate == 1) SB_GATE_VEC(B, true); else SB_GATE_VEC(B, false); }
+#undef SB_GATE_VEC
+    SB_LAUNCH_CHECK();
+    return 0;
+  }
   const size_t total = (size_t)n_rows * cols, want = (total + 255) / 256;
   const int blocks = (int)(want < (size_t)sm_count() * 16 ? want : (size_t)sm_count() * 16);
   if (dtype == SB_DTYPE_F32)

@@ -587,3 +587,106 @@ def test_the_replay_program_on_a_folder_of_this_design(tmp_path, dtype):
                 i += 1
             at[e["id"]] = at.get(e["id"], 0) + len(e["tokens"])
     compare_rows(got, plain, ("cuda", dtype))
+
+
+# ---- configurations nobody chose ---------------------------------------------------------------------------------
+def _random_config(rng) -> dict:
+    """A model of this design drawn at random: widths and vocabularies that are no power of two, 3 to 6 layers in any order with
+    at least one of each mixer, head sizes that are and are not multiples of 16, value heads smaller and larger than the keys',
+    1 to 4 key/value heads, windows from shorter than a page to longer than the prompts, 0 to 70 kept tokens, partial and full
+    rotation with and without scaled frequencies, 2 to 5 taps, 2 to 64 experts with 1 to 8 choices, with and without a shared
+    expert, layers without a feed-forward, with and without the pair table and the cap."""
+    width = rng.choice([72, 96, 100, 128, 136, 200, 264])
+
+    def att():
+        kv = rng.choice([1, 2, 3, 4])
+        dim = rng.choice([16, 24, 32, 40, 64, 80, 128])
+        m = {"heads": kv * rng.choice([1, 2, 4]), "kv_heads": kv, "dim": dim, "vdim": rng.choice([dim, 16, 48, 72]),
+             "scale": rng.choice([2.0, 4.0, 6.0]) / dim}
+        if rng.random() < 0.85:
+            m["mask"] = {"size": rng.choice([1, 7, 40, 64, 65, 130, 1000])}
+            if rng.random() < 0.7:
+                m["mask"]["keep_first"] = rng.choice([0, 1, 4, 6, 33, 70])
+        if rng.random() < 0.85:
+            dims = rng.choice([d for d in (4, 8, 16, 32, 64, 128) if d <= dim] + [dim - dim % 2])
+            m["rot"] = {"base": rng.choice([100.0, 10000.0, 500000.0]), "dims": dims}
+            if rng.random() < 0.6:
+                m["rot"]["scaling"] = {"factor": rng.choice([2.0, 8.0, 32.0]), "low": 1.0, "high": rng.choice([2.0, 4.0]),
+                                       "original": rng.choice([16, 64, 2048])}
+        return m
+
+    def par():
+        kv = rng.choice([1, 2, 4])
+        dim, rdim = rng.choice([16, 32, 48, 64]), rng.choice([8, 16, 32, 64, 128])
+        return {"left": {"heads": kv * rng.choice([1, 2, 3]), "kv_heads": kv, "dim": dim, "vdim": rng.choice([dim, 16, 80]), "scale": 3.0 / dim,
+                         "conv": rng.choice([2, 3, 4, 5]), "mask": {"size": rng.choice([1, 5, 40, 64, 100, 500])}},
+                "right": {"heads": rng.choice([1, 2, 3, 4]), "dim": rdim, "vdim": rng.choice([rdim, 16, 64]), "tau": rng.choice([1.0, 4.0, 16.0, 50.0])},
+                "left_scale": rng.choice([0.5, 0.8, 1.0]), "right_scale": rng.choice([0.5, 1.0, 1.3])}
+
+    def lat():
+        dim, rot = rng.choice([16, 32, 64]), rng.choice([4, 8, 16, 32, 64])
+        return {"heads": rng.choice([1, 2, 3, 4, 8]), "dim": dim, "rot_dim": rot, "vdim": rng.choice([dim, 24, 64]),
+                "kv_rank": rng.choice([16, 24, 40, 64, 100, 192]), "q_rank": rng.choice([8, 20, 48, 96]), "scale": 1.0 / (dim + rot) ** 0.5,
+                "rot": {"base": rng.choice([100.0, 10000.0]), "dims": rot}}
+
+    def mlp():
+        r = rng.random()
+        if r < 0.15:
+            return None
+        if r < 0.4:
+            return DENSE(rng.choice([64, 90, 128, 333]))
+        experts = rng.choice([2, 4, 5, 8, 16, 64])
+        return MOE(experts, rng.choice([t for t in (1, 2, 3, 4, 8) if t <= experts]), rng.choice([16, 24, 64]),
+                   rng.choice([None, 0.5, 1.5, 2.5]), rng.choice([None, 16, 96]))
+
+    kinds = ["attention", "parallel", "latent_attention"] + [rng.choice(["attention", "parallel", "latent_attention"]) for _ in range(rng.randint(0, 3))]
+    rng.shuffle(kinds)
+    make = {"attention": att, "parallel": par, "latent_attention": lat}
+    cfg = {"architecture": "Gebilorn", "width": width, "vocab": rng.choice([131, 257, 500, 640, 1000]), "norm": {"eps": rng.choice([1e-5, 1e-6])},
+           "embedding": {"scale": rng.choice([1.0, 3.0, 8.0])}, "layers": [{"type": k, "mixer": make[k](), "mlp": mlp()} for k in kinds]}
+    if rng.random() < 0.8:
+        cfg["embedding"]["bigram"] = BIGRAM(rng.choice([1, 61, 509, 4099]), rng.choice([0, 7, 127, 1001]), rng.choice([1, 17, 64]))
+    if rng.random() < 0.8:
+        cfg["logit_softcap"] = rng.choice([15.0, 30.0, 50.0])
+    return cfg
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("seed", [1, 2, 3, 4, 5, 6, 7, 8])
+def test_random_configuration(tmp_path, seed, dtype):
+    """Five requests of 2 to 330 tokens in pages of 64, whole, with decoded tails from CUDA graphs, in portions and as mixed batches
+    of four live requests on a pool without a spare page, against the plain implementation."""
+    import random
+
+    rng = random.Random(seed)
+    cfg = _random_config(rng)
+    rank = rng.choice([3, 8, 16])
+    w = make_weights(cfg, seed, rank, expert_gain=0.3)
+    if dtype == "bfloat16":                               # keep routers away from near-ties that 8 bits of the input decide
+        for name in w:
+            if name.endswith(".router"):
+                w[name] = (w[name] * 3.0).bfloat16().float()
+    folder = write_model(str(tmp_path / "m"), cfg, w, getattr(torch, dtype))
+    lens = [rng.choice([2, 3, 17, 64, 65, 130, 200, 257, 330]) for _ in range(5)]
+    reqs = {f"r{i}": helpers.random_tokens(cfg["vocab"], n, seed=seed * 10 + i) for i, n in enumerate(lens)}
+    plain = {rid: plain_logits(w, cfg, toks) for rid, toks in reqs.items()}
+    backend = ("cuda", dtype)
+    cuts = {"whole": helpers.trace_whole, "tail": lambda r: helpers.trace_tail_decode(r, tail=70),
+            "portions": lambda r: helpers.trace_portions(r, sizes=(64, 2, 130, 1, 33, 5)), "mixed": lambda r: helpers.trace_mixed(r, live=4, seed=seed)}
+    for cut, make in cuts.items():
+        steps = make(reqs)
+        pages = helpers.tokens_needed(steps, 64) // 64
+        eng = make_engine(folder, backend, 64, num_pages=pages, max_slots=4, graphs=(cut == "tail"), budget=max(512, pages * 64), context=pages * 64)
+        for v in eng.stepper.views:
+            if v is not None and v.k is not None:
+                v.k.fill_(float("nan"))
+                v.v.fill_(float("nan"))
+        with torch.inference_mode():
+            got = helpers.replay(eng, steps)
+        eng.kernels.check_errors()
+        try:
+            compare_rows(got, plain, backend, allow=len(got) // 8)
+        except AssertionError as e:
+            raise AssertionError(f"{cut}: {json.dumps(cfg)}: {e}") from None
+        assert eng.cache.live == 0

@@ -392,17 +392,17 @@ def gebilorn_at(width: int, vocab: int = 32000):
     from serve_b200.config import config_from_dict
 
     heads, experts, top, ff = DESIGN_SIZES[str(width)]
-    moe = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top, "scale": 1.5}, "shared": {"ff": ff}}
+    moe = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top, "scale": 1.25}, "shared": {"ff": ff}}
     att = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 0.08, "mask": {"size": 1024, "keep_first": 4},
            "rot": {"base": 500000.0, "dims": 64, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
     par = {"left": {"heads": heads // 2, "kv_heads": max(1, heads // 8), "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "conv": 4,
                     "mask": {"size": 1024}},
-           "right": {"heads": heads // 2, "dim": 128, "vdim": 128, "tau": 16.0, "rank": 64}, "left_scale": 0.8, "right_scale": 0.5}
+           "right": {"heads": heads // 2, "dim": 128, "vdim": 128, "tau": 8.0, "rank": 64}, "left_scale": 0.7, "right_scale": 0.6}
     lat = {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 192, "q_rank": 3 * width // 8, "scale": 192 ** -0.5,
            "rot": {"base": 10000.0, "dims": 64}}
     layers = [{"type": "attention", "mixer": att, "mlp": moe}, {"type": "parallel", "mixer": par, "mlp": {"kind": "dense", "ff": top * ff}},
               {"type": "latent_attention", "mixer": lat, "mlp": moe}]
-    return config_from_dict({"architecture": "Gebilorn", "width": width, "vocab": vocab, "norm": {"eps": 1e-5}, "logit_softcap": 30.0,
+    return config_from_dict({"architecture": "Gebilorn", "width": width, "vocab": vocab, "norm": {"eps": 1e-5}, "logit_softcap": 40.0,
                              "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 32003, "mul_cur": 17}}, "layers": layers,
                              "max_position": CONTEXT})
 

@@ -25,10 +25,11 @@ def _number(d, keys, where: str, positive: bool = True) -> None:
             raise ConfigError(f"{where}.{k} must be a {'positive ' if positive else ''}number, got {d[k]!r}")
 
 
-def _check_rot(rot, limit: int, where: str) -> None:
-    _need(rot, ("base", "dims"), where)
+def _check_rot(rot, limit: int, where: str, dims_optional: bool = False) -> None:
+    _need(rot, ("base",) if dims_optional else ("base", "dims"), where)
     _number(rot, ("base",), where)
-    if not isinstance(rot["dims"], int) or rot["dims"] < 0 or rot["dims"] % 2 or rot["dims"] > limit:
+    dims = rot.get("dims", limit)
+    if not isinstance(dims, int) or isinstance(dims, bool) or dims < 0 or dims % 2 or dims > limit:
         raise ConfigError(f"{where}.dims must be even and at most {limit}")
     if rot.get("scaling") is not None:
         _need(rot["scaling"], ("factor", "low", "high", "original"), where + ".scaling")
@@ -77,9 +78,9 @@ def _check_mixer(kind: str, m, where: str) -> None:
         _need(m, ("heads", "dim", "rot_dim", "vdim", "kv_rank", "q_rank", "scale", "rot"), where)
         _positive(m, ("heads", "dim", "rot_dim", "vdim", "kv_rank", "q_rank"), where)
         _number(m, ("scale",), where)
-        _check_rot(m["rot"], m["rot_dim"], where + ".rot")
         if m["rot_dim"] % 2:
             raise ConfigError(f"{where}.rot_dim must be even")
+        _check_rot(m["rot"], m["rot_dim"], where + ".rot", dims_optional=True)      # (rot.dims, if the file names it, may be less than rot_dim)
     else:
         raise ConfigError(f"{where}: type {kind!r} is not known (attention, parallel, latent_attention)")
 

@@ -52,7 +52,7 @@ def _mixer_spec(kind: str, m: dict, width: int, eps: float, prefix: str) -> Part
     sc = rot.get("scaling")
     return PartSpec("latent_attention", {
         "hidden": width, "heads": m["heads"], "dim": m["dim"], "rot_dim": m["rot_dim"], "vdim": m["vdim"], "kv_rank": m["kv_rank"],
-        "q_rank": m["q_rank"], "scale": m["scale"], "rot_base": rot["base"], "rot_dims": m["rot_dim"], "pairing": "half", "eps": eps,
+        "q_rank": m["q_rank"], "scale": m["scale"], "rot_base": rot["base"], "rot_dims": rot.get("dims", m["rot_dim"]), "pairing": "half", "eps": eps,
         "rot_scaling": None if not sc else {"factor": sc["factor"], "low_freq_factor": sc["low"], "high_freq_factor": sc["high"],
                                             "original_max_position_embeddings": sc["original"]}}, prefix)
 

@@ -58,7 +58,7 @@ BIGRAM = lambda buckets, prev, cur: {"buckets": buckets, "mul_prev": prev, "mul_
 CONFIGS = {
     "a": {"architecture": "Gebilorn", "width": 64, "vocab": 150, "norm": {"eps": 1e-5}, "logit_softcap": 12.0,
           "embedding": {"scale": 6.0, "bigram": BIGRAM(61, 7, 13)}, "layers": [
-        {"type": "parallel", "mixer": PAR(4, 2, 24, 16, 0.2, 3, 20, 2, 16, 24, 8.0, 0.7, 0.6), "mlp": MOE(6, 2, 32, 1.5, shared=48)},
+        {"type": "parallel", "mixer": PAR(4, 2, 24, 16, 0.2, 3, 20, 2, 16, 24, 8.0, 0.7, 0.6), "mlp": MOE(6, 2, 32, 1.75, shared=48)},
         {"type": "attention", "mixer": ATT(4, 2, 24, 16, 0.2, 20, 3, 10000.0, 16, (4.0, 1.0, 4.0, 64)), "mlp": DENSE(96)},
         {"type": "latent_attention", "mixer": LAT(4, 16, 8, 24, 40, 28, 0.2, 10000.0), "mlp": None},
         {"type": "attention", "mixer": ATT(2, 2, 16, 32, 0.3, 33, 5, 500.0, 16), "mlp": MOE(4, 1, 48)},
@@ -69,13 +69,13 @@ CONFIGS = {
           "embedding": {"scale": 5.5, "bigram": BIGRAM(1000, 131, 1)}, "layers": [
         {"type": "latent_attention", "mixer": LAT(5, 12, 6, 10, 30, 17, 0.22, 3000.0), "mlp": MOE(5, 3, 22, 0.8, shared=30)},
         {"type": "attention", "mixer": ATT(6, 1, 20, 12, 0.25, 7, None, 3000.0, 10, (8.0, 1.0, 4.0, 32)), "mlp": DENSE(70)},
-        {"type": "parallel", "mixer": PAR(6, 3, 12, 20, 0.3, 4, 50, 3, 12, 20, 16.0, 0.5, 1.25), "mlp": None},
+        {"type": "parallel", "mixer": PAR(6, 3, 12, 20, 0.3, 4, 50, 3, 12, 20, 20.0, 0.5, 1.25), "mlp": None},
         {"type": "attention", "mixer": ATT(3, 3, 12, 20, 0.35, None, None, None, None), "mlp": MOE(3, 3, 30, 2.0)},
     ]},
     # no pair table and no cap; a window far longer than the pages, many kept tokens
     "q": {"architecture": "Gebilorn", "width": 48, "vocab": 97, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0}, "layers": [
         {"type": "attention", "mixer": ATT(6, 3, 8, 8, 0.5, 64, 17, 100.0, 8, (2.0, 1.0, 8.0, 16)), "mlp": MOE(7, 2, 16, shared=16)},
-        {"type": "parallel", "mixer": PAR(3, 1, 16, 8, 0.3, 3, 40, 1, 32, 16, 1.0, 0.9, 0.4), "mlp": DENSE(64)},
+        {"type": "parallel", "mixer": PAR(3, 1, 16, 8, 0.3, 3, 44, 1, 32, 16, 1.0, 0.9, 0.4), "mlp": DENSE(64)},
         {"type": "latent_attention", "mixer": LAT(3, 8, 8, 16, 24, 12, 0.25, 100.0), "mlp": MOE(4, 4, 16, 0.5)},
     ]},
 }
@@ -83,11 +83,11 @@ RANKS = {"a": 8, "o": 5, "q": 12}
 
 # Layers as wide as a real model's: heads of 64 and 128, latent rows of 192 + 64, experts and dense widths that are
 # multiples of 64, so the bfloat16 products run on the tensor-core tiles and the attention on its widest head sizes.
-CONFIGS["wide"] = {"architecture": "Gebilorn", "width": 512, "vocab": 300, "norm": {"eps": 1e-5}, "logit_softcap": 30.0,
-                   "embedding": {"scale": 12.0, "bigram": BIGRAM(509, 127, 17)}, "layers": [
-    {"type": "attention", "mixer": ATT(8, 2, 128, 128, 0.06, 96, 4, 50000.0, 64, (8.0, 1.0, 4.0, 2048)), "mlp": MOE(8, 2, 128, 1.5, shared=128)},
-    {"type": "parallel", "mixer": PAR(8, 4, 64, 64, 0.125, 4, 80, 4, 64, 128, 16.0, 0.8, 0.5), "mlp": DENSE(1024)},
-    {"type": "latent_attention", "mixer": LAT(8, 64, 64, 64, 192, 256, 0.088, 10000.0), "mlp": MOE(8, 2, 128, 1.5)},
+CONFIGS["wide"] = {"architecture": "Gebilorn", "width": 512, "vocab": 300, "norm": {"eps": 1e-5}, "logit_softcap": 25.0,
+                   "embedding": {"scale": 12.0, "bigram": BIGRAM(523, 101, 19)}, "layers": [
+    {"type": "attention", "mixer": ATT(8, 2, 128, 128, 0.06, 96, 4, 200000.0, 64, (4.0, 1.0, 8.0, 1024)), "mlp": MOE(8, 2, 128, 1.25, shared=128)},
+    {"type": "parallel", "mixer": PAR(8, 4, 64, 64, 0.125, 4, 80, 4, 64, 128, 12.0, 0.75, 0.55), "mlp": DENSE(1024)},
+    {"type": "latent_attention", "mixer": LAT(8, 64, 64, 64, 192, 256, 0.088, 10000.0), "mlp": MOE(8, 2, 128, 1.25)},
 ]}
 RANKS["wide"] = 16
 
@@ -99,7 +99,7 @@ def make_weights(cfg: dict, seed: int, rank: int = 8, expert_gain: float = 1.0):
     for name, shape in P.tensor_shapes(cfg, rank).items():
         leaf = name.split(".")[-1]
         if leaf in ("norm1",) or name == "final.norm":
-            t = 0.2 * torch.randn(shape, generator=g)              # stored around zero
+            t = 0.2 * torch.randn(shape, generator=g)              # (the stored weight is its distance from one)
         elif leaf == "norm":
             t = 1.0 + 0.2 * torch.randn(shape, generator=g)
         elif leaf == "sink":

@@ -161,7 +161,7 @@ def parallel_mixer(h, w, p, m, eps):
 def latent_mixer(h, w, p, m, eps):
     heads, dim, rd, vdim, rank = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
     t = h.shape[0]
-    rot = dict(m["rot"], dims=rd)
+    rot = dict(m["rot"], dims=m["rot"].get("dims", rd))
     cq = unit_rms(h @ w[p + "dq"].T, eps) * w[p + "dq.norm"]
     q = (cq @ w[p + "uq"].T).view(t, heads, dim + rd)
     q_plain, q_rot = q[..., :dim], rotate(q[..., dim:], rot)

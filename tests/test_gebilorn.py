@@ -250,12 +250,13 @@ def _mixer_alone(backend, cfg, cuts, seed=5, x=None, tweak=None, page=8, loose=1
 ATTS = [ATT(4, 2, 24, 16, 0.2, 20, 3, 10000.0, 16, (4.0, 1.0, 4.0, 32)), ATT(6, 1, 20, 12, 0.3, 7, None, 3000.0, 10),
         ATT(6, 3, 8, 8, 0.5, 64, 17, 100.0, 8, (8.0, 2.0, 16.0, 64)), ATT(2, 2, 16, 40, 0.25, 9, 9, 500.0, 16),
         ATT(3, 1, 32, 32, 0.12, 1, 2, 7000.0, 32, (2.0, 1.0, 4.0, 16)), ATT(1, 1, 16, 16, 0.3, None, None, None, None)]
-PARS = [PAR(4, 2, 24, 16, 0.2, 3, 20, 2, 16, 24, 8.0, 0.7, 0.6), PAR(6, 3, 12, 20, 0.3, 4, 50, 3, 12, 20, 16.0, 0.5, 1.25),
+PARS = [PAR(4, 2, 24, 16, 0.2, 3, 20, 2, 16, 24, 8.0, 0.7, 0.6), PAR(6, 3, 12, 20, 0.3, 4, 50, 3, 12, 20, 20.0, 0.5, 1.25),
         PAR(3, 1, 16, 8, 0.3, 2, 5, 1, 32, 16, 1.0, 0.9, 0.4), PAR(2, 2, 64, 32, 0.1, 1, 1, 2, 64, 64, 2.5, 1.0, 1.0)]
 LATS = [LAT(4, 16, 8, 24, 40, 28, 0.2, 10000.0), LAT(5, 12, 6, 10, 30, 17, 0.22, 3000.0), LAT(3, 8, 8, 16, 24, 12, 0.25, 100.0),
-        LAT(1, 24, 4, 16, 20, 50, 0.19, 500.0),
+        LAT(1, 24, 4, 16, 20, 50, 0.19, 500.0), dict(LAT(2, 16, 16, 16, 24, 12, 0.2, 1000.0), rot={"base": 1000.0}),      # the file may leave rot.dims out
+        dict(LAT(2, 16, 16, 16, 24, 12, 0.2, 1000.0), rot={"base": 1000.0, "dims": 8}),                                   # or turn a part of the rotated part only
         LAT(2, 16, 8, 16, 264, 20, 0.2, 100.0)]      # a latent row wider than the attention kernels take: keys and values cached per head
-WIDTHS = (64, 100, 48, 40, 72, 56)
+WIDTHS = (64, 100, 48, 40, 72, 56, 64, 80)
 
 
 @pytest.mark.parametrize("backend", BACKENDS)
@@ -316,7 +317,7 @@ def test_dense_feed_forward_alone(backend, ff, width):
 
 
 @pytest.mark.parametrize("backend", BACKENDS)
-@pytest.mark.parametrize("f,width", [(MOE(6, 2, 32, 1.5, shared=48), 64), (MOE(5, 3, 22, 0.8, shared=30), 100), (MOE(4, 1, 48), 48),
+@pytest.mark.parametrize("f,width", [(MOE(6, 2, 32, 1.75, shared=48), 64), (MOE(5, 3, 22, 0.8, shared=30), 100), (MOE(4, 1, 48), 48),
                                      (MOE(3, 3, 30, 2.0), 40), (MOE(1, 1, 16, 3.0, shared=8), 32)])
 def test_experts_alone(backend, f, width):
     """Also: one choice, every expert chosen, one expert in all (whose score is 1, so the weight is the scale itself), no
@@ -454,7 +455,7 @@ def test_one_key_far_back_at_edges_of_pages_windows_and_kept_tokens(backend, cut
 
 @pytest.mark.parametrize("backend", BACKENDS)
 @pytest.mark.parametrize("cuts", [[150], [60, 2, 1, 87], [50] + [1] * 100], ids=["prompt", "portions", "decoded"])
-@pytest.mark.parametrize("size", [1, 2, 40, 64, 65])
+@pytest.mark.parametrize("size", [1, 2, 37, 64, 65])
 def test_convolved_attention_window_edges(backend, cuts, size):
     """The left side's plain window: the key at distance size - 1 is seen, the one at distance size is not."""
     m = PAR(2, 1, 16, 16, 0.6, 2, size, 1, 8, 8, 4.0, 1.0, 1.0)
@@ -604,9 +605,9 @@ def _random_config(rng) -> dict:
         m = {"heads": kv * rng.choice([1, 2, 4]), "kv_heads": kv, "dim": dim, "vdim": rng.choice([dim, 16, 48, 72]),
              "scale": rng.choice([2.0, 4.0, 6.0]) / dim}
         if rng.random() < 0.85:
-            m["mask"] = {"size": rng.choice([1, 7, 40, 64, 65, 130, 1000])}
+            m["mask"] = {"size": rng.choice([1, 7, 38, 64, 65, 130, 1000])}
             if rng.random() < 0.7:
-                m["mask"]["keep_first"] = rng.choice([0, 1, 4, 6, 33, 70])
+                m["mask"]["keep_first"] = rng.choice([0, 1, 4, 5, 33, 70])
         if rng.random() < 0.85:
             dims = rng.choice([d for d in (4, 8, 16, 32, 64, 128) if d <= dim] + [dim - dim % 2])
             m["rot"] = {"base": rng.choice([100.0, 10000.0, 500000.0]), "dims": dims}
@@ -619,8 +620,8 @@ def _random_config(rng) -> dict:
         kv = rng.choice([1, 2, 4])
         dim, rdim = rng.choice([16, 32, 48, 64]), rng.choice([8, 16, 32, 64, 128])
         return {"left": {"heads": kv * rng.choice([1, 2, 3]), "kv_heads": kv, "dim": dim, "vdim": rng.choice([dim, 16, 80]), "scale": 3.0 / dim,
-                         "conv": rng.choice([2, 3, 4, 5]), "mask": {"size": rng.choice([1, 5, 40, 64, 100, 500])}},
-                "right": {"heads": rng.choice([1, 2, 3, 4]), "dim": rdim, "vdim": rng.choice([rdim, 16, 64]), "tau": rng.choice([1.0, 4.0, 16.0, 50.0])},
+                         "conv": rng.choice([2, 3, 4, 5]), "mask": {"size": rng.choice([1, 5, 37, 64, 100, 500])}},
+                "right": {"heads": rng.choice([1, 2, 3, 4]), "dim": rdim, "vdim": rng.choice([rdim, 16, 64]), "tau": rng.choice([1.0, 4.0, 12.0, 50.0])},
                 "left_scale": rng.choice([0.5, 0.8, 1.0]), "right_scale": rng.choice([0.5, 1.0, 1.3])}
 
     def lat():
@@ -643,11 +644,11 @@ def _random_config(rng) -> dict:
     rng.shuffle(kinds)
     make = {"attention": att, "parallel": par, "latent_attention": lat}
     cfg = {"architecture": "Gebilorn", "width": width, "vocab": rng.choice([131, 257, 500, 640, 1000]), "norm": {"eps": rng.choice([1e-5, 1e-6])},
-           "embedding": {"scale": rng.choice([1.0, 3.0, 8.0])}, "layers": [{"type": k, "mixer": make[k](), "mlp": mlp()} for k in kinds]}
+           "embedding": {"scale": rng.choice([1.0, 2.5, 8.0])}, "layers": [{"type": k, "mixer": make[k](), "mlp": mlp()} for k in kinds]}
     if rng.random() < 0.8:
-        cfg["embedding"]["bigram"] = BIGRAM(rng.choice([1, 61, 509, 4099]), rng.choice([0, 7, 127, 1001]), rng.choice([1, 17, 64]))
+        cfg["embedding"]["bigram"] = BIGRAM(rng.choice([1, 61, 523, 4099]), rng.choice([0, 7, 131, 1001]), rng.choice([1, 19, 64]))
     if rng.random() < 0.8:
-        cfg["logit_softcap"] = rng.choice([15.0, 30.0, 50.0])
+        cfg["logit_softcap"] = rng.choice([15.0, 25.0, 50.0])
     return cfg
 
 

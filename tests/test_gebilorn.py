@@ -449,8 +449,8 @@ def test_one_key_far_back_at_edges_of_pages_windows_and_kept_tokens(backend, cut
     seen = [i for i in range(at + 1, n) if P.visible(i, at, size, keep)]
     unseen = [i for i in range(at + 1, n) if not P.visible(i, at, size, keep)]
     assert seen, "the case has no query that sees the key"
-    if unseen:
-        assert float((want[seen[-1]] - want[unseen[0]]).abs().max()) > 4 * _tol(backend, want), "the key does not stand out"
+    if unseen:      # (against the float32 bound: that run is the sharp one; bfloat16's own bound is of the size of the key's share)
+        assert float((want[seen[-1]] - want[unseen[0]]).abs().max()) > 100 * _tol(("", "float32"), want), "the key does not stand out"
 
 
 @pytest.mark.parametrize("backend", BACKENDS)
@@ -477,7 +477,7 @@ def test_convolved_attention_window_edges(backend, cuts, size):
 
     got, want, _ = _mixer_alone(backend, cfg, cuts, x=x, tweak=tweak, page=64, side="left", loose=2.0)
     if 20 + size < n and size > 1:
-        assert float((want[20 + size - 1] - want[20 + size]).abs().max()) > 4 * _tol(backend, want), "the key does not stand out"
+        assert float((want[20 + size - 1] - want[20 + size]).abs().max()) > 100 * _tol(("", "float32"), want), "the key does not stand out"
 
 
 @pytest.mark.parametrize("backend", BACKENDS)
